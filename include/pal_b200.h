@@ -1,0 +1,160 @@
+/*
+ * pal_b200 - C ABI of the B200 (sm_100a) paged-attention operator library.
+ *
+ * This is the boundary a host binding talks to.  It replaces the nanobind/MLX
+ * primitive layer of Proxy Attention Lab (src/pal_core/bindings.cpp:40-222 and the
+ * three Primitive::eval_gpu launchers behind it).  Every entry point takes plain
+ * device pointers and sizes, launches asynchronously on the CUDA stream it is given
+ * (a cudaStream_t passed as void*; NULL = the legacy default stream), never
+ * synchronises, never allocates device memory and owns nothing.
+ *
+ * Error convention: 0 = PAL_OK, negative = error; pal_last_error() returns a
+ * thread-local message for the last failing call on this thread.  No exception or
+ * abort crosses this boundary (the reference throws std::runtime_error /
+ * std::invalid_argument instead: src/pal_core/src/paged_attention_decode_primitive.cpp:139-159).
+ *
+ * Cache layouts (shared with the reference, element type T is 2 bytes, x = 16/sizeof(T) = 8):
+ *   K pool [P, Hkv, D/x, TPP, x]   src/pal_core/src/paged_attention_decode_primitive.cpp:384-397
+ *   V pool [P, Hkv, D,   TPP]      src/pal_core/src/paged_attention_decode_primitive.cpp:373-382
+ * page_table is [S, MP] 32-bit page ids (uint32 in the reference; int32 with the same bits is
+ * accepted), lengths / positions are int32.
+ */
+#ifndef PAL_B200_H_
+#define PAL_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define PAL_OK 0
+#define PAL_ERR_BAD_ARG (-1)     /* null pointer, negative size, Hq % Hkv != 0 ...            */
+#define PAL_ERR_UNSUPPORTED (-2) /* head_dim / tokens_per_page / dtype without an instantiation */
+#define PAL_ERR_LAUNCH (-3)      /* CUDA reported an error at launch                            */
+#define PAL_ERR_WORKSPACE (-4)   /* workspace missing or too small                              */
+#define PAL_ERR_TIMEOUT (-5)     /* a bounded device-side wait gave up (read by pal_check_status) */
+
+#define PAL_DTYPE_F16 0
+#define PAL_DTYPE_BF16 1
+
+/* Value of partition_pages that selects the fused single-pass decode kernel, and the value
+ * that lets the launcher choose (two-pass when the batch alone cannot fill the GPU). */
+#define PAL_DECODE_SINGLE_PASS 0
+#define PAL_DECODE_AUTO (-1)
+
+const char* pal_last_error(void);
+const char* pal_version(void);
+
+/* ---- layout helpers ----------------------------------------------------------------------- */
+/* src/pal_core/bindings.cpp:44-46 (get_k_cache_stripe_size) */
+int pal_get_k_cache_stripe_size(int dtype);
+/* src/pal_core/include/pal_core/constants.hpp:7-11 (get_optimal_page_size) */
+int pal_get_optimal_page_size(void);
+/* src/pal_core/src/paged_attention_decode_primitive.cpp:384-397 (get_k_cache_shape); writes 5 extents */
+int pal_get_k_cache_shape(int64_t num_pages, int num_kv_heads, int head_dim, int tokens_per_page,
+                          int dtype, int64_t shape_out[5]);
+/* src/pal_core/src/paged_attention_decode_primitive.cpp:373-382 (get_v_cache_shape); writes 4 extents */
+int pal_get_v_cache_shape(int64_t num_pages, int num_kv_heads, int head_dim, int tokens_per_page,
+                          int dtype, int64_t shape_out[4]);
+
+/* ---- fill_kv_pages ------------------------------------------------------------------------ */
+/* Replaces FillKVPagesPrimitive::eval_gpu + fill_kv_pages_kernel
+ * (src/pal_core/src/fill_kv_pages_primitive.cpp:70-170,
+ *  src/pal_core/kernels/paged_attention/fill_kv_pages.h.metal:30-121).
+ * Scatters new_keys/new_values [T, Hkv, D] into the pools IN PLACE (the reference copies
+ * both pools first; a caller wanting that clones before the call).  Token t goes to page
+ * page_table[query_to_seq_map[t], pos/TPP], slot pos%TPP with pos = write_positions[t].
+ * Tokens whose page id is >= num_pages, whose sequence index is >= num_seqs or whose
+ * logical block is >= max_pages_per_seq are skipped. */
+int pal_fill_kv_pages(const void* new_keys, const void* new_values, void* k_pool, void* v_pool,
+                      const void* page_table, const int32_t* write_positions,
+                      const void* query_to_seq_map, int64_t num_tokens, int num_seqs,
+                      int num_kv_heads, int head_dim, int tokens_per_page, int64_t num_pages,
+                      int max_pages_per_seq, int dtype, void* stream);
+
+/* Same scatter addressed by flat slot ids: slot_mapping[t] = page * TPP + slot_in_page (int64).
+ * Tokens with a slot outside [0, num_pages*TPP) are skipped.  No counterpart in the reference
+ * (which derives the slot in-kernel, fill_kv_pages.h.metal:64-72); this is the form serving
+ * engines that keep a slot mapping already use. */
+int pal_fill_kv_pages_slots(const void* new_keys, const void* new_values, void* k_pool,
+                            void* v_pool, const int64_t* slot_mapping, int64_t num_tokens,
+                            int num_kv_heads, int head_dim, int tokens_per_page,
+                            int64_t num_pages, int dtype, void* stream);
+
+/* ---- paged_attention_decode --------------------------------------------------------------- */
+/* Bytes of device workspace pal_paged_attention_decode needs for this problem; depends on
+ * partition_pages (see below).  Always >= 256. */
+size_t pal_decode_workspace_bytes(int num_seqs, int num_q_heads, int num_kv_heads, int head_dim,
+                                  int tokens_per_page, int max_pages_per_seq, int partition_pages);
+
+/* Replaces PagedAttentionDecodePrimitive::eval_gpu and its two kernels
+ * (src/pal_core/src/paged_attention_decode_primitive.cpp:71-266,
+ *  src/pal_core/kernels/paged_attention/decode/paged_attention_decode.h.metal:29-412,
+ *  src/pal_core/kernels/paged_attention/decode/paged_reduce_decode.h.metal:27-129).
+ * queries [>=S, Hq, D] (row s belongs to sequence s), out [S, Hq, D] in the query dtype.
+ * A sequence of length <= 0 produces zeros.  scale <= 0 selects 1/sqrt(D).
+ * partition_pages: PAL_DECODE_SINGLE_PASS (0) = one fused pass per (sequence, kv head);
+ * n > 0 = split every sequence into partitions of n pages, write fp32 (m, l, acc) partials to
+ * the workspace and merge them with the log-sum-exp combine kernel; PAL_DECODE_AUTO (-1) lets
+ * the launcher choose.  Page ids are clamped to [0, num_pages) before use. */
+int pal_paged_attention_decode(const void* queries, const void* k_pool, const void* v_pool,
+                               const void* page_table, const int32_t* sequence_lengths, void* out,
+                               int num_seqs, int num_q_heads, int num_kv_heads, int head_dim,
+                               int tokens_per_page, int64_t num_pages, int max_pages_per_seq,
+                               float scale, int dtype, int partition_pages, void* workspace,
+                               size_t workspace_bytes, void* stream);
+
+/* First half of the two-pass decode, for callers that merge partials themselves (for example
+ * across GPUs that each hold a slice of every sequence's context).  Runs the split-KV pass over
+ * the pages this pool holds and merges its own partitions, but does not normalise: writes
+ * m_out [S, Hq] (max scaled score, natural-log units, -inf when the sequence is empty here),
+ * l_out [S, Hq] (sum of exp(score - m)) and acc_out [S, Hq, D] (sum of exp(score - m) * v), fp32.
+ * Shares the workspace rule of pal_paged_attention_decode with the same partition_pages (> 0). */
+int pal_paged_attention_decode_partials(const void* queries, const void* k_pool, const void* v_pool,
+                                        const void* page_table, const int32_t* sequence_lengths,
+                                        float* m_out, float* l_out, float* acc_out, int num_seqs,
+                                        int num_q_heads, int num_kv_heads, int head_dim,
+                                        int tokens_per_page, int64_t num_pages,
+                                        int max_pages_per_seq, float scale, int dtype,
+                                        int partition_pages, void* workspace,
+                                        size_t workspace_bytes, void* stream);
+
+/* Log-sum-exp merge of num_parts partial triples per row (paged_reduce_decode.h.metal:79-128,
+ * with fp32 un-normalised partials instead of the reference's 16-bit pre-normalised ones):
+ * m, l are [num_parts, rows] and acc is [num_parts, rows, D] (part-major, the layout an
+ * all-gather of per-GPU triples produces); out [rows, D] in `dtype`.  A row whose partials are
+ * all empty becomes zeros. */
+int pal_lse_combine(const float* m, const float* l, const float* acc, void* out, int num_parts,
+                    int64_t rows, int head_dim, int dtype, void* stream);
+
+/* ---- paged_attention_prefill -------------------------------------------------------------- */
+size_t pal_prefill_workspace_bytes(int num_seqs, int tokens_per_seq, int num_q_heads,
+                                   int num_kv_heads, int head_dim);
+
+/* Replaces PagedAttentionPrefillPrimitive::eval_gpu and pal_paged_attention_prefill
+ * (src/pal_core/src/paged_attention_prefill_primitive.cpp:63-167,
+ *  src/pal_core/kernels/paged_attention/prefill/paged_attention_prefill.h.metal:28-389).
+ * q_prompt [S*N, Hq, D], k_prompt / v_prompt [S*N, Hkv, D] dense (sequence-major, then token);
+ * history_lens[s] tokens of history are read from the pages; out [S*N*Hq, D], row
+ * (s*N + i)*Hq + h.  Query i sees all history tokens and new tokens 0..i.
+ * impl: 0 = let the launcher choose, 1 = mma.sync kernel (every supported shape),
+ * 2 = tcgen05/TMEM kernel (D = 128, TPP = 16 only; PAL_ERR_UNSUPPORTED otherwise). */
+int pal_paged_attention_prefill(const void* q_prompt, const void* k_prompt, const void* v_prompt,
+                                const void* k_pool, const void* v_pool, const void* page_table,
+                                const int32_t* history_lens, void* out, int num_seqs,
+                                int tokens_per_seq, int num_q_heads, int num_kv_heads, int head_dim,
+                                int tokens_per_page, int64_t num_pages, int max_pages_per_seq,
+                                float scale, int dtype, int impl, void* workspace,
+                                size_t workspace_bytes, void* stream);
+
+/* Reads (with a blocking copy on `stream`) the status word the kernels of the last call that
+ * used `workspace` left there: PAL_OK, or PAL_ERR_TIMEOUT when a bounded device-side wait gave
+ * up.  Optional; intended for tests and debugging. */
+int pal_check_status(const void* workspace, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* PAL_B200_H_ */

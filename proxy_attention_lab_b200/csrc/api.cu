@@ -1,0 +1,392 @@
+// C ABI of the library: argument validation, error strings, and dispatch to the launchers.
+//
+// Stands where the reference has its nanobind module and op builders
+// (src/pal_core/bindings.cpp:40-222, src/pal_core/src/ops.cpp:36-239): shape rules are checked
+// here, before any launch, and failures come back as an error code plus a thread-local message
+// instead of a C++ exception.
+#include <math.h>
+#include <stdarg.h>
+#include <stdio.h>
+
+#include "../../include/pal_b200.h"
+#include "common.cuh"
+#include "launch.h"
+
+namespace pal {
+
+static thread_local char g_error[512] = "";
+
+void set_error(const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_error, sizeof(g_error), fmt, ap);
+  va_end(ap);
+}
+
+static int cuda_rc(int rc, const char* what) {
+  if (rc == 0) return PAL_OK;
+  if (rc < 0) return rc;  // already a PAL_ERR_* with a message
+  set_error("%s: CUDA error %d (%s)", what, rc, cudaGetErrorString((cudaError_t)rc));
+  return PAL_ERR_LAUNCH;
+}
+
+static bool check_dtype(int dtype, const char* what) {
+  if (dtype == PAL_DTYPE_F16 || dtype == PAL_DTYPE_BF16) return true;
+  set_error("%s: dtype %d is not supported (0 = float16, 1 = bfloat16)", what, dtype);
+  return false;
+}
+
+static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+
+static int check_heads(const char* what, int hq, int hkv, int d, int tpp) {
+  if (hq <= 0 || hkv <= 0 || d <= 0 || tpp <= 0) {
+    set_error("%s: head counts, head_dim and tokens_per_page must be positive", what);
+    return PAL_ERR_BAD_ARG;
+  }
+  // src/pal_core/src/paged_attention_decode_primitive.cpp:156-159
+  if (hq % hkv != 0) {
+    set_error("%s: num_q_heads (%d) must be a multiple of num_kv_heads (%d)", what, hq, hkv);
+    return PAL_ERR_BAD_ARG;
+  }
+  return PAL_OK;
+}
+
+}  // namespace pal
+
+using namespace pal;
+
+extern "C" {
+
+const char* pal_last_error(void) { return g_error; }
+const char* pal_version(void) { return "pal_b200 0.1.0 (sm_100a)"; }
+
+int pal_get_k_cache_stripe_size(int dtype) {
+  if (!check_dtype(dtype, "get_k_cache_stripe_size")) return PAL_ERR_UNSUPPORTED;
+  return 16 / 2;
+}
+
+int pal_get_optimal_page_size(void) { return 16; }
+
+int pal_get_k_cache_shape(int64_t num_pages, int num_kv_heads, int head_dim, int tokens_per_page, int dtype,
+                          int64_t shape_out[5]) {
+  if (!check_dtype(dtype, "get_k_cache_shape")) return PAL_ERR_UNSUPPORTED;
+  if (!shape_out) {
+    set_error("get_k_cache_shape: shape_out is null");
+    return PAL_ERR_BAD_ARG;
+  }
+  const int x = 8;
+  shape_out[0] = num_pages;
+  shape_out[1] = num_kv_heads;
+  shape_out[2] = head_dim / x;
+  shape_out[3] = tokens_per_page;
+  shape_out[4] = x;
+  return PAL_OK;
+}
+
+int pal_get_v_cache_shape(int64_t num_pages, int num_kv_heads, int head_dim, int tokens_per_page, int dtype,
+                          int64_t shape_out[4]) {
+  if (!check_dtype(dtype, "get_v_cache_shape")) return PAL_ERR_UNSUPPORTED;
+  if (!shape_out) {
+    set_error("get_v_cache_shape: shape_out is null");
+    return PAL_ERR_BAD_ARG;
+  }
+  shape_out[0] = num_pages;
+  shape_out[1] = num_kv_heads;
+  shape_out[2] = head_dim;
+  shape_out[3] = tokens_per_page;
+  return PAL_OK;
+}
+
+static int fill_common(FillArgs& a, int dtype, void* stream) {
+  if (!check_dtype(dtype, "fill_kv_pages")) return PAL_ERR_UNSUPPORTED;
+  if (a.num_tokens < 0 || a.num_pages < 0) {
+    set_error("fill_kv_pages: negative token or page count");
+    return PAL_ERR_BAD_ARG;
+  }
+  if (a.num_tokens == 0) return PAL_OK;  // src/pal_core/src/fill_kv_pages_primitive.cpp:94-96
+  if (a.num_kv_heads <= 0 || a.head_dim <= 0 || a.tokens_per_page <= 0) {
+    set_error("fill_kv_pages: num_kv_heads, head_dim and tokens_per_page must be positive");
+    return PAL_ERR_BAD_ARG;
+  }
+  // src/pal_core/kernels/paged_attention/fill_kv_pages.h.metal:53,88-94 (16-byte vectors)
+  if (a.head_dim % 8 != 0) {
+    set_error("fill_kv_pages: head_dim (%d) must be a multiple of 8", a.head_dim);
+    return PAL_ERR_UNSUPPORTED;
+  }
+  if (!a.new_keys || !a.new_values || !a.k_pool || !a.v_pool) {
+    set_error("fill_kv_pages: null data pointer");
+    return PAL_ERR_BAD_ARG;
+  }
+  if (!aligned16(a.new_keys) || !aligned16(a.new_values) || !aligned16(a.k_pool) || !aligned16(a.v_pool)) {
+    set_error("fill_kv_pages: data pointers must be 16-byte aligned");
+    return PAL_ERR_BAD_ARG;
+  }
+  return cuda_rc(launch_fill(a, (cudaStream_t)stream), "fill_kv_pages");
+}
+
+int pal_fill_kv_pages(const void* new_keys, const void* new_values, void* k_pool, void* v_pool,
+                      const void* page_table, const int32_t* write_positions, const void* query_to_seq_map,
+                      int64_t num_tokens, int num_seqs, int num_kv_heads, int head_dim, int tokens_per_page,
+                      int64_t num_pages, int max_pages_per_seq, int dtype, void* stream) {
+  FillArgs a{};
+  a.new_keys = new_keys;
+  a.new_values = new_values;
+  a.k_pool = k_pool;
+  a.v_pool = v_pool;
+  a.slot_mapping = nullptr;
+  a.page_table = page_table;
+  a.write_positions = write_positions;
+  a.query_to_seq_map = query_to_seq_map;
+  a.num_tokens = num_tokens;
+  a.num_seqs = num_seqs;
+  a.num_kv_heads = num_kv_heads;
+  a.head_dim = head_dim;
+  a.tokens_per_page = tokens_per_page;
+  a.num_pages = num_pages;
+  a.max_pages_per_seq = max_pages_per_seq;
+  if (num_tokens > 0 && (!page_table || !write_positions || !query_to_seq_map)) {
+    set_error("fill_kv_pages: page_table, write_positions and query_to_seq_map are required");
+    return PAL_ERR_BAD_ARG;
+  }
+  return fill_common(a, dtype, stream);
+}
+
+int pal_fill_kv_pages_slots(const void* new_keys, const void* new_values, void* k_pool, void* v_pool,
+                            const int64_t* slot_mapping, int64_t num_tokens, int num_kv_heads, int head_dim,
+                            int tokens_per_page, int64_t num_pages, int dtype, void* stream) {
+  FillArgs a{};
+  a.new_keys = new_keys;
+  a.new_values = new_values;
+  a.k_pool = k_pool;
+  a.v_pool = v_pool;
+  a.slot_mapping = slot_mapping;
+  a.num_tokens = num_tokens;
+  a.num_kv_heads = num_kv_heads;
+  a.head_dim = head_dim;
+  a.tokens_per_page = tokens_per_page;
+  a.num_pages = num_pages;
+  if (num_tokens > 0 && !slot_mapping) {
+    set_error("fill_kv_pages: slot_mapping is null");
+    return PAL_ERR_BAD_ARG;
+  }
+  return fill_common(a, dtype, stream);
+}
+
+size_t pal_decode_workspace_bytes(int num_seqs, int num_q_heads, int num_kv_heads, int head_dim,
+                                  int tokens_per_page, int max_pages_per_seq, int partition_pages) {
+  if (num_seqs < 0 || num_q_heads <= 0 || num_kv_heads <= 0 || head_dim <= 0) return sizeof(WorkspaceHeader);
+  return decode_workspace_bytes(num_seqs, num_q_heads, num_kv_heads, head_dim, tokens_per_page, max_pages_per_seq,
+                                partition_pages);
+}
+
+static int decode_common(DecodeArgs& a, void* stream, const char* what) {
+  if (!check_dtype(a.dtype, what)) return PAL_ERR_UNSUPPORTED;
+  int rc = check_heads(what, a.num_q_heads, a.num_kv_heads, a.head_dim, a.tokens_per_page);
+  if (rc != PAL_OK) return rc;
+  if (a.num_seqs < 0 || a.num_pages < 0 || a.max_pages_per_seq < 0) {
+    set_error("%s: negative size", what);
+    return PAL_ERR_BAD_ARG;
+  }
+  if (a.num_seqs == 0) return PAL_OK;
+  if (!a.queries || !a.sequence_lengths || (a.num_pages > 0 && (!a.k_pool || !a.v_pool)) ||
+      (a.max_pages_per_seq > 0 && !a.page_table)) {
+    set_error("%s: null input pointer", what);
+    return PAL_ERR_BAD_ARG;
+  }
+  if (!aligned16(a.k_pool) || !aligned16(a.v_pool) || (reinterpret_cast<uintptr_t>(a.queries) & 3)) {
+    set_error("%s: pools must be 16-byte aligned and queries 4-byte aligned", what);
+    return PAL_ERR_BAD_ARG;
+  }
+  if (a.partition_pages < 0)
+    a.partition_pages =
+        decode_auto_partition_pages(a.num_seqs, a.num_q_heads, a.num_kv_heads, a.max_pages_per_seq);
+  if (a.max_pages_per_seq == 0) a.partition_pages = a.m_out ? 1 : 0;
+  const size_t need = decode_workspace_bytes(a.num_seqs, a.num_q_heads, a.num_kv_heads, a.head_dim,
+                                             a.tokens_per_page, a.max_pages_per_seq, a.partition_pages);
+  if (!a.workspace || a.workspace_bytes < need || (reinterpret_cast<uintptr_t>(a.workspace) & 255)) {
+    set_error("%s: workspace of %zu bytes (256-byte aligned) required, got %zu", what, need,
+              a.workspace ? a.workspace_bytes : (size_t)0);
+    return PAL_ERR_WORKSPACE;
+  }
+  if (!(a.scale > 0.f)) a.scale = 1.0f / sqrtf((float)a.head_dim);
+  return cuda_rc(launch_decode(a, (cudaStream_t)stream), what);
+}
+
+int pal_paged_attention_decode(const void* queries, const void* k_pool, const void* v_pool,
+                               const void* page_table, const int32_t* sequence_lengths, void* out, int num_seqs,
+                               int num_q_heads, int num_kv_heads, int head_dim, int tokens_per_page,
+                               int64_t num_pages, int max_pages_per_seq, float scale, int dtype,
+                               int partition_pages, void* workspace, size_t workspace_bytes, void* stream) {
+  DecodeArgs a{};
+  a.queries = queries;
+  a.k_pool = k_pool;
+  a.v_pool = v_pool;
+  a.page_table = static_cast<const uint32_t*>(page_table);
+  a.sequence_lengths = sequence_lengths;
+  a.out = out;
+  a.num_seqs = num_seqs;
+  a.num_q_heads = num_q_heads;
+  a.num_kv_heads = num_kv_heads;
+  a.head_dim = head_dim;
+  a.tokens_per_page = tokens_per_page;
+  a.num_pages = num_pages;
+  a.max_pages_per_seq = max_pages_per_seq;
+  a.scale = scale;
+  a.dtype = dtype;
+  a.partition_pages = partition_pages;
+  a.workspace = workspace;
+  a.workspace_bytes = workspace_bytes;
+  if (num_seqs > 0 && !out) {
+    set_error("paged_attention_decode: out is null");
+    return PAL_ERR_BAD_ARG;
+  }
+  return decode_common(a, stream, "paged_attention_decode");
+}
+
+int pal_paged_attention_decode_partials(const void* queries, const void* k_pool, const void* v_pool,
+                                        const void* page_table, const int32_t* sequence_lengths, float* m_out,
+                                        float* l_out, float* acc_out, int num_seqs, int num_q_heads,
+                                        int num_kv_heads, int head_dim, int tokens_per_page, int64_t num_pages,
+                                        int max_pages_per_seq, float scale, int dtype, int partition_pages,
+                                        void* workspace, size_t workspace_bytes, void* stream) {
+  DecodeArgs a{};
+  a.queries = queries;
+  a.k_pool = k_pool;
+  a.v_pool = v_pool;
+  a.page_table = static_cast<const uint32_t*>(page_table);
+  a.sequence_lengths = sequence_lengths;
+  a.out = nullptr;
+  a.m_out = m_out;
+  a.l_out = l_out;
+  a.acc_out = acc_out;
+  a.num_seqs = num_seqs;
+  a.num_q_heads = num_q_heads;
+  a.num_kv_heads = num_kv_heads;
+  a.head_dim = head_dim;
+  a.tokens_per_page = tokens_per_page;
+  a.num_pages = num_pages;
+  a.max_pages_per_seq = max_pages_per_seq;
+  a.scale = scale;
+  a.dtype = dtype;
+  a.partition_pages = partition_pages;
+  a.workspace = workspace;
+  a.workspace_bytes = workspace_bytes;
+  if (partition_pages <= 0) {
+    set_error("paged_attention_decode_partials: partition_pages must be > 0");
+    return PAL_ERR_BAD_ARG;
+  }
+  if (num_seqs > 0 && (!m_out || !l_out || !acc_out)) {
+    set_error("paged_attention_decode_partials: null output pointer");
+    return PAL_ERR_BAD_ARG;
+  }
+  return decode_common(a, stream, "paged_attention_decode_partials");
+}
+
+int pal_lse_combine(const float* m, const float* l, const float* acc, void* out, int num_parts, int64_t rows,
+                    int head_dim, int dtype, void* stream) {
+  if (!check_dtype(dtype, "lse_combine")) return PAL_ERR_UNSUPPORTED;
+  if (num_parts <= 0 || rows < 0 || head_dim <= 0) {
+    set_error("lse_combine: num_parts and head_dim must be positive, rows non-negative");
+    return PAL_ERR_BAD_ARG;
+  }
+  if (rows == 0) return PAL_OK;
+  if (!m || !l || !acc || !out) {
+    set_error("lse_combine: null pointer");
+    return PAL_ERR_BAD_ARG;
+  }
+  return cuda_rc(launch_lse_combine(m, l, acc, out, nullptr, nullptr, nullptr, num_parts, rows, head_dim, dtype, rows,
+                                    1, rows * head_dim, head_dim, (cudaStream_t)stream),
+                 "lse_combine");
+}
+
+size_t pal_prefill_workspace_bytes(int num_seqs, int tokens_per_seq, int num_q_heads, int num_kv_heads,
+                                   int head_dim) {
+  (void)num_seqs;
+  (void)tokens_per_seq;
+  (void)num_q_heads;
+  (void)num_kv_heads;
+  (void)head_dim;
+  return sizeof(WorkspaceHeader);
+}
+
+int pal_paged_attention_prefill(const void* q_prompt, const void* k_prompt, const void* v_prompt,
+                                const void* k_pool, const void* v_pool, const void* page_table,
+                                const int32_t* history_lens, void* out, int num_seqs, int tokens_per_seq,
+                                int num_q_heads, int num_kv_heads, int head_dim, int tokens_per_page,
+                                int64_t num_pages, int max_pages_per_seq, float scale, int dtype, int impl,
+                                void* workspace, size_t workspace_bytes, void* stream) {
+  const char* what = "paged_attention_prefill";
+  if (!check_dtype(dtype, what)) return PAL_ERR_UNSUPPORTED;
+  int rc = check_heads(what, num_q_heads, num_kv_heads, head_dim, tokens_per_page);
+  if (rc != PAL_OK) return rc;
+  if (num_seqs < 0 || tokens_per_seq < 0 || num_pages < 0 || max_pages_per_seq < 0) {
+    set_error("%s: negative size", what);
+    return PAL_ERR_BAD_ARG;
+  }
+  if (num_seqs == 0 || tokens_per_seq == 0) return PAL_OK;
+  if (!q_prompt || !k_prompt || !v_prompt || !history_lens || !out) {
+    set_error("%s: null pointer", what);
+    return PAL_ERR_BAD_ARG;
+  }
+  if (!aligned16(q_prompt) || !aligned16(k_prompt) || !aligned16(v_prompt) || !aligned16(k_pool) ||
+      !aligned16(v_pool) || !aligned16(out)) {
+    set_error("%s: data pointers must be 16-byte aligned", what);
+    return PAL_ERR_BAD_ARG;
+  }
+  if (!workspace || workspace_bytes < sizeof(WorkspaceHeader) || (reinterpret_cast<uintptr_t>(workspace) & 255)) {
+    set_error("%s: workspace of %zu bytes (256-byte aligned) required", what, sizeof(WorkspaceHeader));
+    return PAL_ERR_WORKSPACE;
+  }
+  PrefillArgs a{};
+  a.q_prompt = q_prompt;
+  a.k_prompt = k_prompt;
+  a.v_prompt = v_prompt;
+  a.k_pool = k_pool;
+  a.v_pool = v_pool;
+  a.page_table = static_cast<const uint32_t*>(page_table);
+  a.history_lens = history_lens;
+  a.out = out;
+  a.num_seqs = num_seqs;
+  a.tokens_per_seq = tokens_per_seq;
+  a.num_q_heads = num_q_heads;
+  a.num_kv_heads = num_kv_heads;
+  a.head_dim = head_dim;
+  a.tokens_per_page = tokens_per_page;
+  a.num_pages = num_pages;
+  a.max_pages_per_seq = max_pages_per_seq;
+  a.scale = scale > 0.f ? scale : 1.0f / sqrtf((float)head_dim);
+  a.dtype = dtype;
+  a.impl = impl;
+  a.workspace = workspace;
+  a.workspace_bytes = workspace_bytes;
+  const bool tc_ok = head_dim == 128 && tokens_per_page == 16;
+  if (impl == 2 && !tc_ok) {
+    set_error("%s: the tcgen05 kernel covers head_dim=128, tokens_per_page=16 only", what);
+    return PAL_ERR_UNSUPPORTED;
+  }
+  if (impl < 0 || impl > 2) {
+    set_error("%s: impl must be 0 (auto), 1 (mma.sync) or 2 (tcgen05)", what);
+    return PAL_ERR_BAD_ARG;
+  }
+  const bool use_tc = impl == 2;
+  return cuda_rc(use_tc ? launch_prefill_tcgen05(a, (cudaStream_t)stream) : launch_prefill_mma(a, (cudaStream_t)stream),
+                 what);
+}
+
+int pal_check_status(const void* workspace, void* stream) {
+  if (!workspace) {
+    set_error("check_status: workspace is null");
+    return PAL_ERR_BAD_ARG;
+  }
+  WorkspaceHeader h;
+  cudaError_t e = cudaMemcpyAsync(&h, workspace, sizeof(h), cudaMemcpyDeviceToHost, (cudaStream_t)stream);
+  if (e == cudaSuccess) e = cudaStreamSynchronize((cudaStream_t)stream);
+  if (e != cudaSuccess) return cuda_rc((int)e, "check_status");
+  if (h.status == kStatusTimeout) {
+    set_error("a bounded device-side wait timed out");
+    return PAL_ERR_TIMEOUT;
+  }
+  return PAL_OK;
+}
+
+}  // extern "C"

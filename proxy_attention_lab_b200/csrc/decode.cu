@@ -1,0 +1,646 @@
+// Paged-attention decode for sm_100a: fused single-pass kernel, split-KV variant and the
+// log-sum-exp combine kernel.
+//
+// Replaces pal_paged_attention_decode (src/pal_core/kernels/paged_attention/decode/
+// paged_attention_decode.h.metal:29-412), pal_paged_reduce_decode (.../paged_reduce_decode.h.metal:27-129)
+// and the launcher PagedAttentionDecodePrimitive::eval_gpu
+// (src/pal_core/src/paged_attention_decode_primitive.cpp:71-266).
+//
+// Design (not a translation of the Metal kernel, which launches one threadgroup per query head and
+// therefore re-reads every KV page Hq/Hkv times):
+//  * One work item = (sequence, kv head, group of <= 8 query heads [, partition]).  The query heads of
+//    a GQA group are the N dimension of the MMAs, so each KV page is read from HBM once per kv head.
+//  * Persistent CTAs pull work items from an atomic counter; in single-pass mode the items are served
+//    longest sequence first (every CTA ranks the sequence lengths in shared memory), which keeps the
+//    tail of a ragged batch short.
+//  * A producer warp walks the page table (32 page ids per coalesced load, one batch prefetched ahead)
+//    and streams each page's contiguous K block and V block (D*TPP*2 bytes each) into a ring of
+//    shared-memory stages with cp.async.bulk + mbarrier transaction counts.  No multicast.
+//  * Four consumer warps take the pages round robin.  Per 16 tokens a warp computes
+//        S^T[16 tok x 8 heads] = K[16 tok x D] . Q^T            (mma.sync m16n8k16, A via ldmatrix)
+//        online softmax over tokens (warp shuffles across the 8 token lanes)
+//        O^T[D x 8 heads]     += V^T[D x 16 tok] . P^T           (A via ldmatrix, B via movmatrix)
+//    The striped K block [D/8][TPP][8] and the transposed V block [D][TPP] are exactly the row-major
+//    8x8 tiles ldmatrix wants, so the pools' native layouts are consumed without any re-tiling.
+//  * The four warps' (m, l, O) are merged through shared memory at the end of an item; in split mode
+//    the merged un-normalised triple goes to the workspace and the combine kernel finishes the job.
+//  * Every mbarrier wait is bounded; on expiry the kernel records a timeout in the workspace status
+//    word and returns.
+#include <math.h>
+
+#include "common.cuh"
+#include "launch.h"
+
+namespace pal {
+
+namespace {
+
+constexpr int kConsumerWarps = 4;
+constexpr int kConsumerThreads = kConsumerWarps * 32;
+constexpr int kDecodeThreads = kConsumerThreads + 32;
+constexpr int kMaxSort = 512;        // rank sequence lengths in-kernel up to this batch size
+constexpr int kHeadsPerItem = 8;     // N of the m16n8k16 MMA
+constexpr int kSmemBudget = 113 * 1024;  // per CTA, so that two CTAs fit one SM
+
+struct DecodeParams {
+  const void* q;
+  const void* k_pool;
+  const void* v_pool;
+  const uint32_t* page_table;
+  const int32_t* seq_lens;
+  void* out;
+  float* part_m;
+  float* part_l;
+  float* part_acc;
+  WorkspaceHeader* hdr;
+  int num_seqs, num_q_heads, num_kv_heads, group, head_groups;
+  int max_pages_per_seq;
+  long long num_pages;
+  int partition_pages, num_parts;
+  int num_items;
+  float scale_log2;
+};
+
+template <int D, int TPP>
+struct DecodeSmem {
+  static constexpr int kBlockBytes = D * TPP * 2;       // one (page, kv head) block of K or of V
+  static constexpr int kStageBytes = 2 * kBlockBytes;
+  static constexpr int kPitch = D + 4;                  // fp32 row pitch of the merge buffer
+  static constexpr int kMergeBytes = kConsumerWarps * kHeadsPerItem * kPitch * 4 + 2 * kConsumerWarps * kHeadsPerItem * 4;
+  static constexpr int kSortBytes = kMaxSort * 4 + kMaxSort * 2;
+  static constexpr int kFixedBytes = kMergeBytes + kSortBytes + 1024;
+  static constexpr int kStagesRaw = (kSmemBudget - kFixedBytes) / kStageBytes;
+  static constexpr int kStages = kStagesRaw > 16 ? 16 : (kStagesRaw < 2 ? 2 : kStagesRaw);
+  static constexpr int kTotalBytes = kStages * kStageBytes + kFixedBytes;
+};
+
+struct ItemCoord {
+  int seq, kvh, hg, part;
+};
+
+template <bool SPLIT>
+__device__ __forceinline__ ItemCoord decode_item(int item, const DecodeParams& p, const uint16_t* sm_order, bool sorted) {
+  ItemCoord c;
+  c.hg = item % p.head_groups;
+  int r = item / p.head_groups;
+  c.kvh = r % p.num_kv_heads;
+  r /= p.num_kv_heads;
+  if (SPLIT) {
+    c.part = r % p.num_parts;
+    c.seq = r / p.num_parts;
+  } else {
+    c.part = 0;
+    c.seq = sorted ? (int)sm_order[r] : r;
+  }
+  return c;
+}
+
+template <bool SPLIT>
+__device__ __forceinline__ void page_range(const DecodeParams& p, int len, int part, int tpp, int& pb, int& pe) {
+  int npages = (len > 0 && p.num_pages > 0) ? (len + tpp - 1) / tpp : 0;
+  if (npages > p.max_pages_per_seq) npages = p.max_pages_per_seq;
+  if (SPLIT) {
+    pb = part * p.partition_pages;
+    pe = min(pb + p.partition_pages, npages);
+    if (pe < pb) pe = pb;
+  } else {
+    pb = 0;
+    pe = npages;
+  }
+}
+
+template <typename T, int D, int TPP, bool SPLIT>
+__global__ void __launch_bounds__(kDecodeThreads, 2) paged_decode_kernel(const DecodeParams p) {
+  using SM = DecodeSmem<D, TPP>;
+  using MMA = Mma16816<T>;
+  constexpr int NST = SM::kStages;
+  constexpr int KSTEPS = D / 16;
+  constexpr int MTILES = D / 16;
+  constexpr int UNITS = TPP / 16;
+
+  extern __shared__ __align__(1024) unsigned char smem[];
+  unsigned char* stages = smem;
+  float* sm_O = reinterpret_cast<float*>(smem + NST * SM::kStageBytes);
+  float* sm_m = sm_O + kConsumerWarps * kHeadsPerItem * SM::kPitch;
+  float* sm_l = sm_m + kConsumerWarps * kHeadsPerItem;
+  int* sm_len = reinterpret_cast<int*>(sm_l + kConsumerWarps * kHeadsPerItem);
+  uint16_t* sm_order = reinterpret_cast<uint16_t*>(sm_len + kMaxSort);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(
+      (reinterpret_cast<uintptr_t>(sm_order + kMaxSort) + 15) & ~uintptr_t(15));
+  uint64_t* full_bar = bars;
+  uint64_t* empty_bar = bars + NST;
+  uint64_t* item_full = bars + 2 * NST;
+  uint64_t* item_empty = item_full + 2;
+  uint64_t* merge_bar = item_empty + 2;  // [0]: all warps wrote their state, [1]: all warps read it
+  int* item_ring = reinterpret_cast<int*>(merge_bar + 2);
+
+  const int tid = threadIdx.x;
+  const int warp = tid >> 5;
+  const int lane = tid & 31;
+  unsigned int* status = &p.hdr->status;
+
+  if (tid == 0) {
+    for (int i = 0; i < NST; ++i) {
+      mbar_init(&full_bar[i], 1);
+      mbar_init(&empty_bar[i], 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&item_full[i], 1);
+      mbar_init(&item_empty[i], kConsumerWarps);
+      mbar_init(&merge_bar[i], kConsumerWarps);
+    }
+    fence_mbar_init();
+  }
+  const bool sorted = !SPLIT && p.num_seqs <= kMaxSort;
+  if (sorted) {
+    for (int s = tid; s < p.num_seqs; s += kDecodeThreads) sm_len[s] = p.seq_lens[s];
+    __syncthreads();
+    for (int s = tid; s < p.num_seqs; s += kDecodeThreads) {
+      const int ls = sm_len[s];
+      int rank = 0;
+      for (int j = 0; j < p.num_seqs; ++j) {
+        const int lj = sm_len[j];
+        rank += (lj > ls) || (lj == ls && j < s);
+      }
+      sm_order[rank] = (uint16_t)s;
+    }
+  }
+  __syncthreads();
+
+  if (warp == kConsumerWarps) {
+    // ------------------------------ producer warp ------------------------------
+    const unsigned char* kp = static_cast<const unsigned char*>(p.k_pool);
+    const unsigned char* vp = static_cast<const unsigned char*>(p.v_pool);
+    uint32_t n_item = 0, it = 0;
+    for (;;) {
+      int item = 0;
+      if (lane == 0) item = (int)atomicAdd(&p.hdr->work_counter, 1u);
+      item = __shfl_sync(0xffffffffu, item, 0);
+      int ok = 1;
+      if (lane == 0) {
+        const int slot = n_item & 1;
+        ok = mbar_wait(&item_empty[slot], ((n_item >> 1) & 1) ^ 1, status);
+        if (ok) {
+          item_ring[slot] = item;
+          mbar_arrive(&item_full[slot]);
+        }
+      }
+      ok = __shfl_sync(0xffffffffu, ok, 0);
+      if (!ok) return;
+      ++n_item;
+      if (item >= p.num_items) break;
+
+      const ItemCoord c = decode_item<SPLIT>(item, p, sm_order, sorted);
+      const int len = sorted ? sm_len[c.seq] : p.seq_lens[c.seq];
+      int pb, pe;
+      page_range<SPLIT>(p, len, c.part, TPP, pb, pe);
+      const int npg = pe - pb;
+      const uint32_t* row = p.page_table + (size_t)c.seq * p.max_pages_per_seq + pb;
+      uint32_t pid_next = lane < npg ? row[lane] : 0u;
+      for (int j0 = 0; j0 < npg; j0 += 32) {
+        const uint32_t pid_cur = pid_next;
+        if (j0 + 32 + lane < npg) pid_next = row[j0 + 32 + lane];
+        const int cnt = min(32, npg - j0);
+        for (int k = 0; k < cnt; ++k) {
+          uint32_t pid = __shfl_sync(0xffffffffu, pid_cur, k);
+          if (lane == 0 && ok) {
+            const uint32_t n = it + j0 + k;
+            const uint32_t stage = n % NST;
+            ok = mbar_wait(&empty_bar[stage], ((n / NST) & 1) ^ 1, status);
+            if (ok) {
+              if ((long long)pid >= p.num_pages) pid = (uint32_t)(p.num_pages - 1);
+              const size_t off = ((size_t)pid * p.num_kv_heads + c.kvh) * SM::kBlockBytes;
+              unsigned char* dst = stages + stage * SM::kStageBytes;
+              mbar_arrive_expect_tx(&full_bar[stage], SM::kStageBytes);
+              bulk_g2s(dst, kp + off, SM::kBlockBytes, &full_bar[stage]);
+              bulk_g2s(dst + SM::kBlockBytes, vp + off, SM::kBlockBytes, &full_bar[stage]);
+            }
+          }
+        }
+        ok = __shfl_sync(0xffffffffu, ok, 0);
+        if (!ok) return;
+      }
+      it += npg;
+    }
+    return;
+  }
+
+  // -------------------------------- consumer warps --------------------------------
+  const int g = lane >> 2;
+  const int t = lane & 3;
+  const T* qbase = static_cast<const T*>(p.q);
+  uint32_t n_item = 0, it = 0, n_merge = 0;
+  for (;;) {
+    const int slot = n_item & 1;
+    if (!mbar_wait(&item_full[slot], (n_item >> 1) & 1, status)) return;
+    const int item = item_ring[slot];
+    __syncwarp();
+    if (lane == 0) mbar_arrive(&item_empty[slot]);
+    ++n_item;
+    if (item >= p.num_items) break;
+
+    const ItemCoord c = decode_item<SPLIT>(item, p, sm_order, sorted);
+    const int len = sorted ? sm_len[c.seq] : p.seq_lens[c.seq];
+    int pb, pe;
+    page_range<SPLIT>(p, len, c.part, TPP, pb, pe);
+    const int npg = pe - pb;
+    const int head0 = c.kvh * p.group + c.hg * kHeadsPerItem;
+    const int nheads = min(kHeadsPerItem, p.group - c.hg * kHeadsPerItem);
+
+    // Q^T as the B operand: b0 = Q[head g][16ks + 2t, +1], b1 = Q[head g][16ks + 8 + 2t, +1]
+    uint32_t qf[KSTEPS][2];
+    {
+      const bool valid = g < nheads;
+      const uint32_t* qrow =
+          reinterpret_cast<const uint32_t*>(qbase + ((size_t)c.seq * p.num_q_heads + head0 + (valid ? g : 0)) * D);
+#pragma unroll
+      for (int ks = 0; ks < KSTEPS; ++ks) {
+        qf[ks][0] = valid ? qrow[ks * 8 + t] : 0u;
+        qf[ks][1] = valid ? qrow[ks * 8 + 4 + t] : 0u;
+      }
+    }
+    float m_run[2] = {-INFINITY, -INFINITY};
+    float l_run[2] = {0.f, 0.f};
+    float o[MTILES][4];
+#pragma unroll
+    for (int i = 0; i < MTILES; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+
+    for (int j = warp; j < npg; j += kConsumerWarps) {
+      const uint32_t n = it + j;
+      const uint32_t stage = n % NST;
+      if (!mbar_wait(&full_bar[stage], (n / NST) & 1, status)) return;
+      const uint32_t kb = smem_u32(stages + stage * SM::kStageBytes);
+      const uint32_t vb = kb + SM::kBlockBytes;
+      const int tok0 = (pb + j) * TPP;
+#pragma unroll
+      for (int u = 0; u < UNITS; ++u) {
+        const int nvalid = len - (tok0 + 16 * u);
+        if (nvalid <= 0) break;
+        // ---- S^T = K . Q^T ----
+        float s[4] = {0.f, 0.f, 0.f, 0.f};
+        {
+          // matrix i = lane/8: chunk 2ks + (i>>1), tokens 8*(i&1) + lane%8
+          const int mi = lane >> 3, r = lane & 7;
+          const uint32_t a_lane = kb + (uint32_t)((mi >> 1) * (TPP * 16) + (16 * u + (mi & 1) * 8 + r) * 16);
+#pragma unroll
+          for (int ks = 0; ks < KSTEPS; ++ks) {
+            uint32_t a[4];
+            ldmatrix_x4(a, a_lane + ks * 2 * (TPP * 16));
+            MMA::run(s, a, qf[ks][0], qf[ks][1]);
+          }
+        }
+        // s[0],s[1]: token g, heads 2t,2t+1;  s[2],s[3]: token g+8
+        const bool v_lo = g < nvalid, v_hi = g + 8 < nvalid;
+        s[0] = v_lo ? s[0] * p.scale_log2 : -INFINITY;
+        s[1] = v_lo ? s[1] * p.scale_log2 : -INFINITY;
+        s[2] = v_hi ? s[2] * p.scale_log2 : -INFINITY;
+        s[3] = v_hi ? s[3] * p.scale_log2 : -INFINITY;
+        float mx0 = fmaxf(s[0], s[2]), mx1 = fmaxf(s[1], s[3]);
+#pragma unroll
+        for (int sh = 4; sh <= 16; sh <<= 1) {
+          mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, sh));
+          mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, sh));
+        }
+        const float mn0 = fmaxf(m_run[0], mx0), mn1 = fmaxf(m_run[1], mx1);
+        // token 0 of a processed unit is always valid, so mn0/mn1 are finite here unless the
+        // data itself is non-finite
+        const float c0 = fast_exp2(m_run[0] - mn0), c1 = fast_exp2(m_run[1] - mn1);
+        m_run[0] = mn0;
+        m_run[1] = mn1;
+        const float p0 = fast_exp2(s[0] - mn0), p1 = fast_exp2(s[1] - mn1);
+        const float p2 = fast_exp2(s[2] - mn0), p3 = fast_exp2(s[3] - mn1);
+        l_run[0] = l_run[0] * c0 + p0 + p2;
+        l_run[1] = l_run[1] * c1 + p1 + p3;
+        if (__any_sync(0xffffffffu, c0 != 1.f || c1 != 1.f)) {
+#pragma unroll
+          for (int i = 0; i < MTILES; ++i) {
+            o[i][0] *= c0;
+            o[i][1] *= c1;
+            o[i][2] *= c0;
+            o[i][3] *= c1;
+          }
+        }
+        // P^T as the B operand of the PV MMA
+        const uint32_t b0 = movmatrix_trans(MMA::pack(p0, p1));
+        const uint32_t b1 = movmatrix_trans(MMA::pack(p2, p3));
+        // ---- O^T += V^T . P^T ----
+        {
+          // matrix i = lane/8: d rows 8*(i&1) + lane%8 of the m-tile, token half i>>1
+          const int mi = lane >> 3, r = lane & 7;
+          const uint32_t a_lane = vb + (uint32_t)(((mi & 1) * 8 + r) * (TPP * 2) + 32 * u + (mi >> 1) * 16);
+          uint32_t mask_lo = 0xffffffffu, mask_hi = 0xffffffffu;
+          if (nvalid < 16) {
+            // a0/a1 hold tokens 2t,2t+1 and a2/a3 tokens 2t+8,2t+9: zero what lies past the length
+            const int ta = 2 * t, tb = 2 * t + 8;
+            mask_lo = (ta < nvalid ? 0x0000ffffu : 0u) | (ta + 1 < nvalid ? 0xffff0000u : 0u);
+            mask_hi = (tb < nvalid ? 0x0000ffffu : 0u) | (tb + 1 < nvalid ? 0xffff0000u : 0u);
+          }
+#pragma unroll
+          for (int mt = 0; mt < MTILES; ++mt) {
+            uint32_t a[4];
+            ldmatrix_x4(a, a_lane + mt * 16 * (TPP * 2));
+            if (nvalid < 16) {
+              a[0] &= mask_lo;
+              a[1] &= mask_lo;
+              a[2] &= mask_hi;
+              a[3] &= mask_hi;
+            }
+            MMA::run(o[mt], a, b0, b1);
+          }
+        }
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&empty_bar[stage]);
+    }
+    it += npg;
+
+    // ---- merge the four warps' partial states ----
+#pragma unroll
+    for (int sh = 4; sh <= 16; sh <<= 1) {
+      l_run[0] += __shfl_xor_sync(0xffffffffu, l_run[0], sh);
+      l_run[1] += __shfl_xor_sync(0xffffffffu, l_run[1], sh);
+    }
+    if (g == 0) {
+      sm_m[warp * kHeadsPerItem + 2 * t] = m_run[0];
+      sm_m[warp * kHeadsPerItem + 2 * t + 1] = m_run[1];
+      sm_l[warp * kHeadsPerItem + 2 * t] = l_run[0];
+      sm_l[warp * kHeadsPerItem + 2 * t + 1] = l_run[1];
+    }
+    {
+      float* ow = sm_O + warp * kHeadsPerItem * SM::kPitch;
+#pragma unroll
+      for (int mt = 0; mt < MTILES; ++mt) {
+        ow[(2 * t) * SM::kPitch + 16 * mt + g] = o[mt][0];
+        ow[(2 * t + 1) * SM::kPitch + 16 * mt + g] = o[mt][1];
+        ow[(2 * t) * SM::kPitch + 16 * mt + g + 8] = o[mt][2];
+        ow[(2 * t + 1) * SM::kPitch + 16 * mt + g + 8] = o[mt][3];
+      }
+    }
+    // consumer-only barrier built on an mbarrier so that, like every other wait here, it is bounded
+    __syncwarp();
+    if (lane == 0) mbar_arrive(&merge_bar[0]);
+    if (!mbar_wait(&merge_bar[0], n_merge & 1, status)) return;
+    for (int idx = tid; idx < nheads * D; idx += kConsumerThreads) {
+      const int h = idx / D, d = idx - h * D;
+      float mw[kConsumerWarps];
+      float M = -INFINITY;
+#pragma unroll
+      for (int w = 0; w < kConsumerWarps; ++w) {
+        mw[w] = sm_m[w * kHeadsPerItem + h];
+        M = fmaxf(M, mw[w]);
+      }
+      float num = 0.f, den = 0.f;
+      if (M > -INFINITY) {
+#pragma unroll
+        for (int w = 0; w < kConsumerWarps; ++w) {
+          const float wgt = fast_exp2(mw[w] - M);
+          num += wgt * sm_O[(w * kHeadsPerItem + h) * SM::kPitch + d];
+          den += wgt * sm_l[w * kHeadsPerItem + h];
+        }
+      }
+      const size_t row = (size_t)c.seq * p.num_q_heads + head0 + h;
+      if (SPLIT) {
+        const size_t prow = row * p.num_parts + c.part;
+        p.part_acc[prow * D + d] = num;
+        if (d == 0) {
+          p.part_m[prow] = M > -INFINITY ? M * kLn2 : -INFINITY;
+          p.part_l[prow] = den;
+        }
+      } else {
+        static_cast<T*>(p.out)[row * D + d] = MMA::from_float(den > 0.f ? num / den : 0.f);
+      }
+    }
+    __syncwarp();
+    if (lane == 0) mbar_arrive(&merge_bar[1]);
+    if (!mbar_wait(&merge_bar[1], n_merge & 1, status)) return;
+    ++n_merge;
+  }
+}
+
+// Merge num_parts partial triples per row.  One CTA per row, one thread per head-dim element pair.
+// m/l/acc are addressed with explicit strides so the same kernel serves the in-workspace layout
+// [row][part] and the part-major layout [part][row] of gathered per-GPU triples.
+template <typename T>
+__global__ void __launch_bounds__(128) lse_combine_kernel(const float* __restrict__ m, const float* __restrict__ l,
+                                                          const float* __restrict__ acc, T* __restrict__ out,
+                                                          float* __restrict__ m_out, float* __restrict__ l_out,
+                                                          float* __restrict__ acc_out, int num_parts, int head_dim,
+                                                          long long part_stride_ml, long long row_stride_ml,
+                                                          long long part_stride_acc, long long row_stride_acc) {
+  const long long row = blockIdx.x;
+  const float* mr = m + row * row_stride_ml;
+  const float* lr = l + row * row_stride_ml;
+  __shared__ float s_w[1024];
+  __shared__ float s_red[8];
+  // pass 1: global max over partitions
+  float mx = -INFINITY;
+  for (int j = threadIdx.x; j < num_parts; j += blockDim.x) mx = fmaxf(mx, mr[j * part_stride_ml]);
+#pragma unroll
+  for (int sh = 16; sh >= 1; sh >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, sh));
+  if ((threadIdx.x & 31) == 0) s_red[threadIdx.x >> 5] = mx;
+  __syncthreads();
+  float M = s_red[0];
+  for (int w = 1; w < (int)(blockDim.x >> 5); ++w) M = fmaxf(M, s_red[w]);
+  __syncthreads();
+  // pass 2: weights and denominator
+  float den = 0.f;
+  for (int j = threadIdx.x; j < num_parts; j += blockDim.x) {
+    const float mj = mr[j * part_stride_ml];
+    const float w = (mj > -INFINITY) ? __expf(mj - M) : 0.f;
+    if (j < 1024) s_w[j] = w;
+    den += w * lr[j * part_stride_ml];
+  }
+#pragma unroll
+  for (int sh = 16; sh >= 1; sh >>= 1) den += __shfl_xor_sync(0xffffffffu, den, sh);
+  if ((threadIdx.x & 31) == 0) s_red[threadIdx.x >> 5] = den;
+  __syncthreads();
+  float den_all = 0.f;
+  for (int w = 0; w < (int)(blockDim.x >> 5); ++w) den_all += s_red[w];
+  const float* ar = acc + row * row_stride_acc;
+  for (int d = threadIdx.x; d < head_dim; d += blockDim.x) {
+    float num = 0.f;
+    for (int j = 0; j < num_parts; ++j) {
+      float w;
+      if (j < 1024) {
+        w = s_w[j];
+      } else {
+        const float mj = mr[j * part_stride_ml];
+        w = (mj > -INFINITY) ? __expf(mj - M) : 0.f;
+      }
+      if (w != 0.f) num += w * ar[j * part_stride_acc + d];
+    }
+    if (out) {
+      const float v = den_all > 0.f ? num / den_all : 0.f;
+      out[row * head_dim + d] = Mma16816<T>::from_float(v);
+    }
+    if (acc_out) acc_out[row * head_dim + d] = num;
+  }
+  if (threadIdx.x == 0 && m_out) {
+    m_out[row] = M;
+    l_out[row] = den_all;
+  }
+}
+
+template <typename T, int D, int TPP, bool SPLIT>
+int launch_decode_inst(const DecodeParams& p, int num_sms, cudaStream_t stream) {
+  using SM = DecodeSmem<D, TPP>;
+  static_assert(SM::kTotalBytes <= 227 * 1024, "decode shared memory exceeds the per-CTA limit");
+  auto kern = paged_decode_kernel<T, D, TPP, SPLIT>;
+  static bool configured[64] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 64 && !configured[dev]) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SM::kTotalBytes);
+    if (e != cudaSuccess) return (int)e;
+    configured[dev] = true;
+  }
+  const int ctas_per_sm = SM::kTotalBytes <= kSmemBudget ? 2 : 1;
+  int grid = num_sms * ctas_per_sm;
+  if (grid > p.num_items) grid = p.num_items;
+  if (grid < 1) grid = 1;
+  kern<<<grid, kDecodeThreads, SM::kTotalBytes, stream>>>(p);
+  return (int)cudaGetLastError();
+}
+
+template <typename T, bool SPLIT>
+int dispatch_shape(const DecodeParams& p, int head_dim, int tpp, int num_sms, cudaStream_t stream) {
+#define PAL_DECODE_CASE(DD, TT) \
+  if (head_dim == DD && tpp == TT) return launch_decode_inst<T, DD, TT, SPLIT>(p, num_sms, stream);
+  PAL_DECODE_CASE(32, 16)
+  PAL_DECODE_CASE(64, 16)
+  PAL_DECODE_CASE(80, 16)
+  PAL_DECODE_CASE(96, 16)
+  PAL_DECODE_CASE(128, 16)
+  PAL_DECODE_CASE(256, 16)
+  PAL_DECODE_CASE(32, 32)
+  PAL_DECODE_CASE(64, 32)
+  PAL_DECODE_CASE(80, 32)
+  PAL_DECODE_CASE(96, 32)
+  PAL_DECODE_CASE(128, 32)
+  PAL_DECODE_CASE(256, 32)
+#undef PAL_DECODE_CASE
+  set_error("paged_attention_decode: no kernel for head_dim=%d tokens_per_page=%d "
+            "(head_dim in {32,64,80,96,128,256}, tokens_per_page in {16,32})", head_dim, tpp);
+  return -2;
+}
+
+int cached_sm_count() {
+  static int sms[64] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev >= 64) return 148;
+  if (sms[dev] == 0) {
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+    sms[dev] = n;
+  }
+  return sms[dev];
+}
+
+size_t align256(size_t x) { return (x + 255) & ~size_t(255); }
+
+}  // namespace
+
+int decode_num_partitions(int max_pages_per_seq, int partition_pages) {
+  if (partition_pages <= 0) return 1;
+  int n = (max_pages_per_seq + partition_pages - 1) / partition_pages;
+  return n < 1 ? 1 : n;
+}
+
+// Two-pass when the batch alone cannot give every SM a couple of work items; partitions are sized so
+// that roughly four items per SM exist, but never smaller than 16 pages.
+int decode_auto_partition_pages(int num_seqs, int num_q_heads, int num_kv_heads, int max_pages_per_seq) {
+  const int group = num_q_heads / num_kv_heads;
+  const long long items = (long long)num_seqs * num_kv_heads * ((group + kHeadsPerItem - 1) / kHeadsPerItem);
+  const long long want = 148LL * 4;
+  if (items >= 148LL * 2 || max_pages_per_seq <= 32) return 0;
+  long long parts = (want + items - 1) / items;
+  long long pp = (max_pages_per_seq + parts - 1) / parts;
+  if (pp < 16) pp = 16;
+  if (pp >= max_pages_per_seq) return 0;
+  return (int)pp;
+}
+
+size_t decode_workspace_bytes(int num_seqs, int num_q_heads, int num_kv_heads, int head_dim, int tokens_per_page,
+                              int max_pages_per_seq, int partition_pages) {
+  (void)tokens_per_page;
+  if (partition_pages < 0)
+    partition_pages = decode_auto_partition_pages(num_seqs, num_q_heads, num_kv_heads, max_pages_per_seq);
+  size_t bytes = sizeof(WorkspaceHeader);
+  if (partition_pages > 0) {
+    const size_t rows = (size_t)num_seqs * num_q_heads * decode_num_partitions(max_pages_per_seq, partition_pages);
+    bytes += 2 * align256(rows * 4) + align256(rows * head_dim * 4);
+  }
+  return bytes;
+}
+
+int launch_lse_combine(const float* m, const float* l, const float* acc, void* out, float* m_out, float* l_out,
+                       float* acc_out, int num_parts, long long rows, int head_dim, int dtype, long long part_stride_ml,
+                       long long row_stride_ml, long long part_stride_acc, long long row_stride_acc,
+                       cudaStream_t stream) {
+  if (rows == 0) return 0;
+  if (dtype == 0)
+    lse_combine_kernel<__half><<<(unsigned)rows, 128, 0, stream>>>(m, l, acc, (__half*)out, m_out, l_out, acc_out,
+                                                                   num_parts, head_dim, part_stride_ml, row_stride_ml,
+                                                                   part_stride_acc, row_stride_acc);
+  else
+    lse_combine_kernel<__nv_bfloat16><<<(unsigned)rows, 128, 0, stream>>>(
+        m, l, acc, (__nv_bfloat16*)out, m_out, l_out, acc_out, num_parts, head_dim, part_stride_ml, row_stride_ml,
+        part_stride_acc, row_stride_acc);
+  return (int)cudaGetLastError();
+}
+
+int launch_decode(const DecodeArgs& a, cudaStream_t stream) {
+  DecodeParams p;
+  p.q = a.queries;
+  p.k_pool = a.k_pool;
+  p.v_pool = a.v_pool;
+  p.page_table = a.page_table;
+  p.seq_lens = a.sequence_lengths;
+  p.out = a.out;
+  p.hdr = static_cast<WorkspaceHeader*>(a.workspace);
+  p.num_seqs = a.num_seqs;
+  p.num_q_heads = a.num_q_heads;
+  p.num_kv_heads = a.num_kv_heads;
+  p.group = a.num_q_heads / a.num_kv_heads;
+  p.head_groups = (p.group + kHeadsPerItem - 1) / kHeadsPerItem;
+  p.max_pages_per_seq = a.max_pages_per_seq;
+  p.num_pages = a.num_pages;
+  p.partition_pages = a.partition_pages;
+  p.num_parts = decode_num_partitions(a.max_pages_per_seq, a.partition_pages);
+  p.scale_log2 = a.scale * kLog2e;
+  const bool split = a.partition_pages > 0;
+  const long long items =
+      (long long)a.num_seqs * a.num_kv_heads * p.head_groups * (split ? p.num_parts : 1);
+  if (items > 0x7fffffffLL) {
+    set_error("paged_attention_decode: too many work items (%lld)", items);
+    return -1;
+  }
+  p.num_items = (int)items;
+  const size_t rows = (size_t)a.num_seqs * a.num_q_heads * p.num_parts;
+  unsigned char* ws = static_cast<unsigned char*>(a.workspace);
+  p.part_m = reinterpret_cast<float*>(ws + sizeof(WorkspaceHeader));
+  p.part_l = reinterpret_cast<float*>(ws + sizeof(WorkspaceHeader) + align256(rows * 4));
+  p.part_acc = reinterpret_cast<float*>(ws + sizeof(WorkspaceHeader) + 2 * align256(rows * 4));
+
+  cudaError_t e = cudaMemsetAsync(a.workspace, 0, 8, stream);
+  if (e != cudaSuccess) return (int)e;
+  const int sms = cached_sm_count();
+  int rc;
+  if (a.dtype == 0)
+    rc = split ? dispatch_shape<__half, true>(p, a.head_dim, a.tokens_per_page, sms, stream)
+               : dispatch_shape<__half, false>(p, a.head_dim, a.tokens_per_page, sms, stream);
+  else
+    rc = split ? dispatch_shape<__nv_bfloat16, true>(p, a.head_dim, a.tokens_per_page, sms, stream)
+               : dispatch_shape<__nv_bfloat16, false>(p, a.head_dim, a.tokens_per_page, sms, stream);
+  if (rc != 0) return rc;
+  if (split) {
+    const long long out_rows = (long long)a.num_seqs * a.num_q_heads;
+    rc = launch_lse_combine(p.part_m, p.part_l, p.part_acc, a.out, a.m_out, a.l_out, a.acc_out, p.num_parts, out_rows,
+                            a.head_dim, a.dtype, 1, p.num_parts, a.head_dim, (long long)p.num_parts * a.head_dim,
+                            stream);
+  }
+  return rc;
+}
+
+}  // namespace pal

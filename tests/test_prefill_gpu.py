@@ -1,0 +1,94 @@
+"""GPU parity of paged_attention_prefill against the CPU oracle (through the C ABI)."""
+
+import pytest
+import torch
+
+from cases import make_prefill_case, max_abs, to_dev
+from oracle import prefill_oracle
+
+pytestmark = pytest.mark.gpu
+
+TOL = 2e-3
+
+
+def run_prefill(pal, case, device, **kw):
+    t = to_dev(case, device)
+    out = pal.paged_attention_prefill(t["q"], t["k_new"], t["v_new"], t["k_pool"], t["v_pool"], t["page_table"], t["hist"], **kw)
+    torch.cuda.synchronize()
+    return out.cpu()
+
+
+def check(pal, cuda, case, impl, tol=TOL):
+    ref = prefill_oracle(case.q, case.k_new, case.v_new, case.k_pool, case.v_pool, case.page_table, case.hist)
+    out = run_prefill(pal, case, cuda, impl=impl)
+    assert out.shape == ref.shape and out.dtype == case.q.dtype
+    assert torch.isfinite(out.float()).all()
+    # Early causal rows attend to one or two keys, so |out| reaches a few units and the rounding of the
+    # 16-bit output alone exceeds 2e-3; the kernel is therefore also compared with the oracle rounded to
+    # the output dtype, allowing one unit in the last place there.
+    diff = (out.float() - ref).abs()
+    ulp = torch.maximum(ref.abs(), torch.tensor(1e-3)) * (2.0 ** -7 if out.dtype == torch.bfloat16 else 2.0 ** -10)
+    bad = (diff > tol) & (diff > ulp)
+    assert not bad.any(), f"max-abs {diff.max().item()} with {int(bad.sum())} elements out of tolerance"
+
+
+IMPLS = ["mma"]
+
+
+@pytest.mark.parametrize("impl", IMPLS)
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize(
+    "batch,hist,n,heads,d",
+    [(1, 0, 16, (4, 4), 64), (1, 128, 16, (4, 4), 64), (2, 64, 32, (8, 2), 128), (1, 256, 1, (32, 8), 128), (1, 0, 128, (32, 8), 128)],
+)
+def test_reference_shape_list(pal, cuda, impl, dtype, batch, hist, n, heads, d):
+    """Shape list of tests/paged_attention/prefill/test_sdpa_equivalency.py:21-27."""
+    case = make_prefill_case(5, [hist] * batch, n, heads[0], heads[1], d, dtype=dtype)
+    check(pal, cuda, case, impl)
+
+
+@pytest.mark.parametrize("impl", IMPLS)
+@pytest.mark.parametrize("d", [32, 64, 80, 96, 128, 256])
+@pytest.mark.parametrize("tpp", [16, 32])
+def test_head_dims_and_page_sizes(pal, cuda, impl, d, tpp):
+    case = make_prefill_case(9, [0, 70, 129], 77, 4, 2, d, tpp=tpp, dtype=torch.bfloat16)
+    check(pal, cuda, case, impl)
+
+
+@pytest.mark.parametrize("impl", IMPLS)
+def test_ragged_history_with_poisoned_padding(pal, cuda, impl):
+    case = make_prefill_case(13, [0, 1, 15, 16, 17, 300], 130, 8, 2, 128, dtype=torch.bfloat16, poison_unused=True)
+    check(pal, cuda, case, impl)
+
+
+@pytest.mark.parametrize("impl", IMPLS)
+def test_llama8b_shape_reduced(pal, cuda, impl):
+    """Llama-3-8B head shape, 2 sequences x 512 new tokens over ragged history."""
+    case = make_prefill_case(0, [1000, 37], 512, 32, 8, 128, dtype=torch.bfloat16)
+    check(pal, cuda, case, impl)
+
+
+@pytest.mark.parametrize("impl", IMPLS)
+def test_no_history_empty_pool(pal, cuda, impl):
+    """tests/paged_attention/prefill/test_softmax_and_value.py:72-78: zero-page pools and an (S, 0) page table."""
+    dtype, d = torch.float16, 64
+    q = torch.ones((1, 1, d), dtype=dtype, device=cuda)
+    k = torch.ones((1, 1, d), dtype=dtype, device=cuda)
+    v = torch.zeros((1, 1, d), dtype=dtype, device=cuda)
+    v[0, 0, :4] = torch.tensor([10.0, 20.0, 30.0, 40.0], dtype=dtype)
+    kp = torch.zeros(pal.get_k_cache_shape(0, 1, d, 16, dtype), dtype=dtype, device=cuda)
+    vp = torch.zeros(pal.get_v_cache_shape(0, 1, d, 16, dtype), dtype=dtype, device=cuda)
+    pt = torch.zeros((1, 0), dtype=torch.int32, device=cuda)
+    out = pal.paged_attention_prefill(q, k, v, kp, vp, pt, torch.zeros(1, dtype=torch.int32, device=cuda), impl=impl)
+    assert out.shape == (1, d)
+    assert torch.equal(out[0].cpu(), v[0, 0].cpu())
+
+
+@pytest.mark.parametrize("impl", IMPLS)
+@pytest.mark.parametrize("n,hist", [(64, 64), (256, 1024), (1024, 64)])
+def test_determinism(pal, cuda, impl, n, hist):
+    """tests/paged_attention/prefill/test_determinism.py:16-127."""
+    case = make_prefill_case(21, [hist], n, 8, 2, 128, dtype=torch.bfloat16)
+    a = run_prefill(pal, case, cuda, impl=impl)
+    b = run_prefill(pal, case, cuda, impl=impl)
+    assert torch.equal(a, b)
