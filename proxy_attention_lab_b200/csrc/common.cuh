@@ -112,6 +112,8 @@ struct Mma16816<__half> {
     __half2 h = __floats2half2_rn(lo, hi);
     return *reinterpret_cast<uint32_t*>(&h);
   }
+  static constexpr bool kSplitP = false;
+  __device__ static __forceinline__ uint32_t pack_residual(float, float, uint32_t) { return 0u; }
   __device__ static __forceinline__ float to_float(__half v) { return __half2float(v); }
   __device__ static __forceinline__ __half from_float(float v) { return __float2half_rn(v); }
 };
@@ -125,6 +127,11 @@ struct Mma16816<__nv_bfloat16> {
   __device__ static __forceinline__ uint32_t pack(float lo, float hi) {
     __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
     return *reinterpret_cast<uint32_t*>(&h);
+  }
+  static constexpr bool kSplitP = true;
+  // bf16 pair of (lo - bf16(lo), hi - bf16(hi)), given the already packed bf16 pair
+  __device__ static __forceinline__ uint32_t pack_residual(float lo, float hi, uint32_t packed) {
+    return pack(lo - __uint_as_float(packed << 16), hi - __uint_as_float(packed & 0xffff0000u));
   }
   __device__ static __forceinline__ float to_float(__nv_bfloat16 v) { return __bfloat162float(v); }
   __device__ static __forceinline__ __nv_bfloat16 from_float(float v) { return __float2bfloat16_rn(v); }

@@ -69,8 +69,10 @@ struct DecodeSmem {
   static constexpr int kMergeBytes = kConsumerWarps * kHeadsPerItem * kPitch * 4 + 2 * kConsumerWarps * kHeadsPerItem * 4;
   static constexpr int kSortBytes = kMaxSort * 4 + kMaxSort * 2;
   static constexpr int kFixedBytes = kMergeBytes + kSortBytes + 1024;
-  static constexpr int kStagesRaw = (kSmemBudget - kFixedBytes) / kStageBytes;
-  static constexpr int kStages = kStagesRaw > 16 ? 16 : (kStagesRaw < 2 ? 2 : kStagesRaw);
+  // A stage is always consumed by warp (stage % 4): the ring length is a multiple of the consumer
+  // warp count, so a warp meets the phases of its own stages strictly in order.
+  static constexpr int kStagesRaw = ((kSmemBudget - kFixedBytes) / kStageBytes) / kConsumerWarps * kConsumerWarps;
+  static constexpr int kStages = kStagesRaw > 16 ? 16 : (kStagesRaw < kConsumerWarps ? kConsumerWarps : kStagesRaw);
   static constexpr int kTotalBytes = kStages * kStageBytes + kFixedBytes;
 };
 
@@ -265,7 +267,8 @@ __global__ void __launch_bounds__(kDecodeThreads, 2) paged_decode_kernel(const D
 #pragma unroll
     for (int i = 0; i < MTILES; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
 
-    for (int j = warp; j < npg; j += kConsumerWarps) {
+    // page n (counted over the whole kernel) belongs to warp n % 4 and lives in stage n % NST
+    for (int j = (warp - (int)(it & 3)) & 3; j < npg; j += kConsumerWarps) {
       const uint32_t n = it + j;
       const uint32_t stage = n % NST;
       if (!mbar_wait(&full_bar[stage], (n / NST) & 1, status)) return;
@@ -320,9 +323,16 @@ __global__ void __launch_bounds__(kDecodeThreads, 2) paged_decode_kernel(const D
             o[i][3] *= c1;
           }
         }
-        // P^T as the B operand of the PV MMA
-        const uint32_t b0 = movmatrix_trans(MMA::pack(p0, p1));
-        const uint32_t b1 = movmatrix_trans(MMA::pack(p2, p3));
+        // P^T as the B operand of the PV MMA.  bf16 keeps only 8 bits of P, so there the residual
+        // P - bf16(P) goes through a second MMA and the product is accurate to ~2^-17.
+        const uint32_t pk0 = MMA::pack(p0, p1), pk1 = MMA::pack(p2, p3);
+        const uint32_t b0 = movmatrix_trans(pk0);
+        const uint32_t b1 = movmatrix_trans(pk1);
+        uint32_t r0 = 0, r1 = 0;
+        if (MMA::kSplitP) {
+          r0 = movmatrix_trans(MMA::pack_residual(p0, p1, pk0));
+          r1 = movmatrix_trans(MMA::pack_residual(p2, p3, pk1));
+        }
         // ---- O^T += V^T . P^T ----
         {
           // matrix i = lane/8: d rows 8*(i&1) + lane%8 of the m-tile, token half i>>1
@@ -346,6 +356,7 @@ __global__ void __launch_bounds__(kDecodeThreads, 2) paged_decode_kernel(const D
               a[3] &= mask_hi;
             }
             MMA::run(o[mt], a, b0, b1);
+            if (MMA::kSplitP) MMA::run(o[mt], a, r0, r1);
           }
         }
       }

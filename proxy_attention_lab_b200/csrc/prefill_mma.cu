@@ -232,6 +232,14 @@ __global__ void __launch_bounds__(kPrefillThreads) prefill_mma_kernel(const Pref
       a[1] = MMA::pack(sacc[2 * kk][2], sacc[2 * kk][3]);
       a[2] = MMA::pack(sacc[2 * kk + 1][0], sacc[2 * kk + 1][1]);
       a[3] = MMA::pack(sacc[2 * kk + 1][2], sacc[2 * kk + 1][3]);
+      // bf16 keeps 8 bits of P; the residual P - bf16(P) goes through a second MMA (see decode.cu)
+      uint32_t ar[4] = {0u, 0u, 0u, 0u};
+      if (MMA::kSplitP) {
+        ar[0] = MMA::pack_residual(sacc[2 * kk][0], sacc[2 * kk][1], a[0]);
+        ar[1] = MMA::pack_residual(sacc[2 * kk][2], sacc[2 * kk][3], a[1]);
+        ar[2] = MMA::pack_residual(sacc[2 * kk + 1][0], sacc[2 * kk + 1][1], a[2]);
+        ar[3] = MMA::pack_residual(sacc[2 * kk + 1][2], sacc[2 * kk + 1][3], a[3]);
+      }
 #pragma unroll
       for (int nd = 0; nd < NDT; nd += 2) {
         uint32_t b[4];
@@ -248,6 +256,10 @@ __global__ void __launch_bounds__(kPrefillThreads) prefill_mma_kernel(const Pref
         }
         MMA::run(o[nd], a, b[0], b[1]);
         MMA::run(o[nd + 1], a, b[2], b[3]);
+        if (MMA::kSplitP) {
+          MMA::run(o[nd], ar, b[0], b[1]);
+          MMA::run(o[nd + 1], ar, b[2], b[3]);
+        }
       }
     }
   }

@@ -1,0 +1,93 @@
+"""The C-ABI library loads, exports every symbol the header declares, and validates arguments
+before it touches a device (no GPU needed: none of these calls reaches a kernel launch)."""
+
+import ctypes
+import re
+from pathlib import Path
+
+import pytest
+import torch
+
+ROOT = Path(__file__).resolve().parent.parent
+
+
+def declared_symbols():
+    text = (ROOT / "include" / "pal_b200.h").read_text()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(pal_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_header_symbols_are_exported_and_bound():
+    from proxy_attention_lab_b200 import _lib
+
+    names = declared_symbols()
+    assert len(names) >= 14
+    for name in names:
+        assert hasattr(_lib.lib, name), f"{name} is declared in the header but not exported"
+        assert name in _lib.SIGNATURES, f"{name} has no ctypes signature"
+    assert sorted(_lib.SIGNATURES) == names
+
+
+def test_layout_helpers():
+    import proxy_attention_lab_b200 as pal
+    from oracle import k_cache_shape, k_cache_stripe_size, v_cache_shape
+
+    for dtype in (torch.float16, torch.bfloat16):
+        assert pal.get_k_cache_stripe_size(dtype) == k_cache_stripe_size(dtype) == 8
+        assert pal.get_k_cache_shape(7, 2, 128, 16, dtype) == k_cache_shape(7, 2, 128, 16, dtype) == (7, 2, 16, 16, 8)
+        assert pal.get_v_cache_shape(7, 2, 128, 16, dtype) == v_cache_shape(7, 2, 128, 16, dtype) == (7, 2, 128, 16)
+    assert pal.get_optimal_page_size() == 16
+    assert pal.pal_core.get_optimal_page_size() == 16
+    with pytest.raises(ValueError):
+        pal.get_k_cache_stripe_size(torch.float32)
+
+
+def test_reference_names_are_exported():
+    import proxy_attention_lab_b200 as pal
+
+    for name in ("fill_kv_pages", "paged_attention_decode", "paged_attention_prefill", "get_k_cache_shape",
+                 "get_v_cache_shape", "get_k_cache_stripe_size", "get_optimal_page_size"):
+        assert callable(getattr(pal, name)) and callable(getattr(pal.pal_core, name))
+
+
+def test_validation_errors_come_back_as_codes():
+    from proxy_attention_lab_b200 import _lib
+
+    lib = _lib.lib
+    # dtype 7 does not exist
+    rc = lib.pal_get_k_cache_stripe_size(7)
+    assert rc == _lib.PAL_ERR_UNSUPPORTED and "dtype" in _lib.last_error()
+    rc = lib.pal_fill_kv_pages_slots(None, None, None, None, None, 1, 1, 64, 16, 1, 0, None)
+    assert rc == _lib.PAL_ERR_BAD_ARG and "slot_mapping" in _lib.last_error()
+    # Hq not a multiple of Hkv
+    dummy = ctypes.create_string_buffer(64)  # only has to be non-null: validation fails before any use
+    rc = lib.pal_paged_attention_decode(None, None, None, None, None, ctypes.addressof(dummy), 1, 3, 2, 64, 16, 1, 1, 0.0, 0, 0,
+                                        None, 0, None)
+    assert rc == _lib.PAL_ERR_BAD_ARG and "multiple" in _lib.last_error()
+    # null pointers
+    rc = lib.pal_paged_attention_decode(None, None, None, None, None, None, 1, 2, 2, 64, 16, 1, 1, 0.0, 0, 0, None, 0, None)
+    assert rc == _lib.PAL_ERR_BAD_ARG
+    # zero work is fine and launches nothing
+    assert lib.pal_fill_kv_pages_slots(None, None, None, None, None, 0, 1, 64, 16, 1, 0, None) == _lib.PAL_OK
+    assert lib.pal_paged_attention_decode(None, None, None, None, None, None, 0, 2, 2, 64, 16, 1, 1, 0.0, 0, 0, None, 0, None) == _lib.PAL_OK
+    # workspace sizing: header only for the single pass, partials for the two-pass form
+    assert lib.pal_decode_workspace_bytes(8, 64, 8, 128, 16, 8192, 0) == 256
+    two_pass = lib.pal_decode_workspace_bytes(8, 64, 8, 128, 16, 8192, 256)
+    rows = 8 * 64 * 32
+    assert two_pass >= 256 + rows * (128 + 2) * 4
+    with pytest.raises(RuntimeError):
+        _lib.check(_lib.PAL_ERR_UNSUPPORTED)
+    with pytest.raises(ValueError):
+        _lib.check(_lib.PAL_ERR_BAD_ARG)
+
+
+def test_cpu_tensors_are_rejected():
+    import proxy_attention_lab_b200 as pal
+
+    q = torch.zeros((1, 2, 64), dtype=torch.float16)
+    k = torch.zeros((1, 2, 8, 16, 8), dtype=torch.float16)
+    v = torch.zeros((1, 2, 64, 16), dtype=torch.float16)
+    with pytest.raises(RuntimeError, match="no CPU path"):
+        pal.paged_attention_decode(q, k, v, torch.zeros((1, 1), dtype=torch.int32), torch.ones(1, dtype=torch.int32))
+    with pytest.raises(RuntimeError, match="no CPU path"):
+        pal.fill_kv_pages(q, q, k, v, torch.zeros(1, dtype=torch.int64))

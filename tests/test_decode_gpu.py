@@ -23,12 +23,13 @@ def check(pal, cuda, case, tol=TOL, **kw):
     out = run_decode(pal, case, cuda, **kw)
     assert out.shape == ref.shape and out.dtype == case.q.dtype
     assert torch.isfinite(out.float()).all()
-    # compare against the oracle rounded to the output dtype as well: the rounding of the output
-    # itself is not an error of the kernel
-    err = max_abs(out, ref)
-    err_q = max_abs(out, ref.to(out.dtype))
-    assert min(err, err_q) <= tol, f"max-abs {err} (vs rounded oracle {err_q})"
-    return err
+    # An element passes when it is within 2e-3 of the fp32 oracle, or within one unit in the last
+    # place of the 16-bit output type: once |out| >= 0.5 the rounding of a bf16 output alone exceeds 2e-3.
+    diff = (out.float() - ref).abs()
+    ulp = torch.maximum(ref.abs(), torch.tensor(1e-3)) * (2.0 ** -7 if out.dtype == torch.bfloat16 else 2.0 ** -10)
+    bad = (diff > tol) & (diff > ulp)
+    assert not bad.any(), f"max-abs {diff.max().item()}, {int(bad.sum())} elements out of tolerance"
+    return diff.max().item()
 
 
 def test_cpu_equivalence_config(pal, cuda):
