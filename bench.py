@@ -1,0 +1,510 @@
+#!/usr/bin/env python
+"""Benchmark of the paged-attention hot path on B200.
+
+``python bench.py --gpus N --steps K --warmup W`` prints ONE JSON line (rank 0).  A step is one pass
+of the operator over one batch of synthetic input already resident in HBM.  The default workload is
+the Llama-3-8B-shaped decode batch the headline metric (paged decode KV GB/s) is quoted on; other
+workloads (``--workload decode_70b | prefill_8b | fill``) cover the remaining configurations.
+
+``--impl reference`` times the reference side of the comparison instead.  Proxy Attention Lab has no
+CPU implementation and its Metal kernels cannot run here, so that arm is the CPU oracle (the
+restatement of the reference test-suite's gather-pages + SDPA comparator) on all host threads.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import math
+import os
+import sys
+import threading
+import time
+
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+WORKLOADS = {
+    # name: (kind, params)
+    "decode_8b": dict(kind="decode", S=64, lo=1024, hi=8192, hq=32, hkv=8, d=128, tpp=16, partition_pages=0,
+                      desc="Llama-3-8B decode: batch 64, context U[1024,8192], 32q/8kv heads, D=128, bf16, TPP=16, fused single pass"),
+    "decode_70b": dict(kind="decode", S=8, lo=131072, hi=131072, hq=64, hkv=8, d=128, tpp=16, partition_pages=256,
+                       desc="Llama-3-70B long decode: batch 8, context 131072, 64q/8kv heads, D=128, bf16, TPP=16, two-pass 256-page partitions"),
+    "prefill_8b": dict(kind="prefill", S=8, n=2048, hlo=0, hhi=4096, hq=32, hkv=8, d=128, tpp=16,
+                       desc="Llama-3-8B chunked causal prefill: 8 x 2048 new tokens, history U[0,4096], 32q/8kv heads, D=128, bf16, TPP=16"),
+    "fill": dict(kind="fill", S=64, n=512, hkv=8, d=128, tpp=16, pages=65536,
+                 desc="fill_kv_pages: 64 x 512 tokens, 8 kv heads, D=128, bf16, TPP=16, 65536-page pool, random free slots"),
+}
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        with open(path) as f:
+            p = json.load(f)
+        return dict(hbm=float(p["hbm_gbs"]), tensor=float(p["bf16_tflops"]), tensor_sustained=float(p.get("bf16_tflops_sustained", p["bf16_tflops"])), source="measured")
+    except Exception:
+        return dict(hbm=6650.0, tensor=1590.0, tensor_sustained=1400.0, source="fallback")
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons through NVML (read-only) while a region runs."""
+
+    def __init__(self, index: int, period_s: float = 0.01):
+        self.index, self.period = index, period_s
+        self.samples, self.reasons = [], set()
+        self.max_mhz = None
+        self._stop = threading.Event()
+        self._thread = None
+        try:
+            import pynvml
+
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            self.h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM)
+        except Exception:
+            self.nv = None
+
+    def _reason_names(self, mask):
+        nv = self.nv
+        table = [("hw_slowdown", "nvmlClocksThrottleReasonHwSlowdown"), ("hw_thermal_slowdown", "nvmlClocksThrottleReasonHwThermalSlowdown"),
+                 ("sw_thermal_slowdown", "nvmlClocksThrottleReasonSwThermalSlowdown"), ("sw_power_cap", "nvmlClocksThrottleReasonSwPowerCap"),
+                 ("hw_power_brake", "nvmlClocksThrottleReasonHwPowerBrakeSlowdown")]
+        out = []
+        for name, attr in table:
+            bit = getattr(nv, attr, None)
+            if bit is not None and mask & bit:
+                out.append(name)
+        return out
+
+    def _once(self):
+        try:
+            self.samples.append(self.nv.nvmlDeviceGetClockInfo(self.h, self.nv.NVML_CLOCK_SM))
+            self.reasons.update(self._reason_names(self.nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.h)))
+        except Exception:
+            pass
+
+    def _run(self):
+        while not self._stop.is_set():
+            self._once()
+            self._stop.wait(self.period)
+
+    def __enter__(self):
+        if self.nv is not None:
+            self._thread = threading.Thread(target=self._run, daemon=True)
+            self._thread.start()
+        return self
+
+    def __exit__(self, *a):
+        if self._thread is not None:
+            self._once()
+            self._stop.set()
+            self._thread.join()
+
+    def summary(self):
+        if not self.samples:
+            return {"sm_mhz": None, "sm_max_mhz": self.max_mhz, "reasons": ["unavailable"]}
+        s = sorted(self.samples)
+        return {"sm_mhz": s[len(s) // 2], "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons), "samples": len(s)}
+
+
+# ------------------------------------------------------------------------------------------------
+# synthetic workloads
+# ------------------------------------------------------------------------------------------------
+def make_lengths(seed, count, lo, hi):
+    g = torch.Generator().manual_seed(seed)
+    return torch.randint(lo, hi + 1, (count,), generator=g)
+
+
+def build_decode(cfg, device, seed, hkv_local=None):
+    """Device-resident decode batch: shuffled page pool sized to the total tokens."""
+    tpp, d, hq = cfg["tpp"], cfg["d"], cfg["hq"]
+    hkv = hkv_local or cfg["hkv"]
+    hq_local = hq * hkv // cfg["hkv"]
+    lens = make_lengths(seed, cfg["S"], cfg["lo"], cfg["hi"])
+    npg = (lens + tpp - 1) // tpp
+    P, MP = int(npg.sum()), int(npg.max())
+    g = torch.Generator().manual_seed(seed + 1)
+    perm = torch.randperm(P, generator=g)
+    table = torch.zeros((cfg["S"], MP), dtype=torch.int32)
+    off = 0
+    for s in range(cfg["S"]):
+        n = int(npg[s])
+        table[s, :n] = perm[off:off + n].to(torch.int32)
+        off += n
+    gen = torch.Generator(device=device).manual_seed(seed + 2)
+    k_pool = torch.randn((P, hkv, d // 8, tpp, 8), device=device, dtype=torch.bfloat16, generator=gen)
+    v_pool = torch.randn((P, hkv, d, tpp), device=device, dtype=torch.bfloat16, generator=gen)
+    q_host = torch.randn((cfg["S"], hq_local, d), generator=g).to(torch.bfloat16).pin_memory()
+    table_host = table.pin_memory()
+    lens_host = lens.to(torch.int32).pin_memory()
+    total_tokens = int(lens.sum())
+    kv_bytes = total_tokens * hkv * d * 2 * 2
+    alg_bytes = kv_bytes + 2 * cfg["S"] * hq_local * d * 2 + 4 * int(npg.sum()) + 4 * cfg["S"]
+    if cfg["partition_pages"]:
+        parts = (MP + cfg["partition_pages"] - 1) // cfg["partition_pages"]
+        alg_bytes += 2 * cfg["S"] * hq_local * parts * (d + 2) * 4
+    return dict(k_pool=k_pool, v_pool=v_pool, q_host=q_host, table_host=table_host, lens_host=lens_host,
+                q=q_host.to(device), table=table_host.to(device), lens=lens_host.to(device), kv_bytes=kv_bytes,
+                alg_bytes=alg_bytes, tokens=cfg["S"], hq=hq_local, hkv=hkv, lens_cpu=lens)
+
+
+def build_prefill(cfg, device, seed, seqs=None):
+    tpp, d, hq, hkv, n = cfg["tpp"], cfg["d"], cfg["hq"], cfg["hkv"], cfg["n"]
+    hist_all = make_lengths(seed, cfg["S"], cfg["hlo"], cfg["hhi"])
+    idx = list(range(cfg["S"])) if seqs is None else seqs
+    hist = hist_all[idx]
+    S = len(idx)
+    npg = (hist + tpp - 1) // tpp
+    P, MP = max(int(npg.sum()), 1), max(int(npg.max()), 1)
+    g = torch.Generator().manual_seed(seed + 1)
+    perm = torch.randperm(P, generator=g)
+    table = torch.zeros((S, MP), dtype=torch.int32)
+    off = 0
+    for s in range(S):
+        m = int(npg[s])
+        table[s, :m] = perm[off:off + m].to(torch.int32)
+        off += m
+    gen = torch.Generator(device=device).manual_seed(seed + 2)
+    mk = lambda *shape: torch.randn(shape, device=device, dtype=torch.bfloat16, generator=gen)
+    data = dict(k_pool=mk(P, hkv, d // 8, tpp, 8), v_pool=mk(P, hkv, d, tpp), q=mk(S * n, hq, d), k=mk(S * n, hkv, d), v=mk(S * n, hkv, d),
+                table=table.to(device), hist=hist.to(torch.int32).to(device))
+    data["flops"] = 4 * hq * d * sum(n * int(h) + n * (n + 1) // 2 for h in hist)
+    data["tokens"] = S * n
+    data["hist_cpu"] = hist
+    return data
+
+
+def build_fill(cfg, device, seed):
+    tpp, d, hkv = cfg["tpp"], cfg["d"], cfg["hkv"]
+    T, P = cfg["S"] * cfg["n"], cfg["pages"]
+    gen = torch.Generator(device=device).manual_seed(seed)
+    keys = torch.randn((T, hkv, d), device=device, dtype=torch.bfloat16, generator=gen)
+    vals = torch.randn((T, hkv, d), device=device, dtype=torch.bfloat16, generator=gen)
+    g = torch.Generator().manual_seed(seed + 1)
+    slots = torch.randperm(P * tpp, generator=g)[:T]
+    k_pool = torch.zeros((P, hkv, d // 8, tpp, 8), device=device, dtype=torch.bfloat16)
+    v_pool = torch.zeros((P, hkv, d, tpp), device=device, dtype=torch.bfloat16)
+    return dict(keys=keys, vals=vals, slots=slots.to(device), k_pool=k_pool, v_pool=v_pool, alg_bytes=4 * T * hkv * d * 2 + 8 * T, tokens=T,
+                keys_host=keys.cpu().pin_memory(), vals_host=vals.cpu().pin_memory(), slots_host=slots.pin_memory())
+
+
+# ------------------------------------------------------------------------------------------------
+# CPU side (oracle) - the reference arm and the cpu_baseline leg
+# ------------------------------------------------------------------------------------------------
+def cpu_decode_sample(cfg, budget_s, seed=0):
+    """Times the oracle on the first sequences of the workload until `budget_s` is spent. Returns (bytes, seconds, n_seqs)."""
+    from oracle import decode_oracle
+
+    tpp, d, hq, hkv = cfg["tpp"], cfg["d"], cfg["hq"], cfg["hkv"]
+    lens = make_lengths(seed, cfg["S"], cfg["lo"], cfg["hi"])
+    g = torch.Generator().manual_seed(seed + 7)
+    done_bytes, spent, nseq = 0, 0.0, 0
+    for s in range(cfg["S"]):
+        L = int(lens[s])
+        if L * hkv * d * 4 > 8e9:  # keep one sequence's fp32 copy within host memory
+            L = int(8e9 // (hkv * d * 4))
+        npg = (L + tpp - 1) // tpp
+        k_pool = torch.randn((npg, hkv, d // 8, tpp, 8), generator=g).to(torch.bfloat16)
+        v_pool = torch.randn((npg, hkv, d, tpp), generator=g).to(torch.bfloat16)
+        q = torch.randn((1, hq, d), generator=g).to(torch.bfloat16)
+        table = torch.randperm(npg, generator=g).reshape(1, npg).to(torch.int32)
+        t0 = time.perf_counter()
+        decode_oracle(q, k_pool, v_pool, table, torch.tensor([L], dtype=torch.int32))
+        spent += time.perf_counter() - t0
+        done_bytes += L * hkv * d * 2 * 2
+        nseq += 1
+        if spent >= budget_s:
+            break
+    return done_bytes, spent, nseq
+
+
+def cpu_prefill_sample(cfg, budget_s, seed=0):
+    from oracle import prefill_oracle
+
+    tpp, d, hq, hkv = cfg["tpp"], cfg["d"], cfg["hq"], cfg["hkv"]
+    n = min(cfg["n"], 512)  # a 512-token slice of one sequence keeps the score matrix small
+    hist = int(make_lengths(seed, cfg["S"], cfg["hlo"], cfg["hhi"])[0])
+    g = torch.Generator().manual_seed(seed + 7)
+    npg = max((hist + tpp - 1) // tpp, 1)
+    k_pool = torch.randn((npg, hkv, d // 8, tpp, 8), generator=g).to(torch.bfloat16)
+    v_pool = torch.randn((npg, hkv, d, tpp), generator=g).to(torch.bfloat16)
+    q = torch.randn((n, hq, d), generator=g).to(torch.bfloat16)
+    k = torch.randn((n, hkv, d), generator=g).to(torch.bfloat16)
+    v = torch.randn((n, hkv, d), generator=g).to(torch.bfloat16)
+    table = torch.randperm(npg, generator=g).reshape(1, npg).to(torch.int32)
+    flops, spent, reps = 0, 0.0, 0
+    while spent < budget_s:
+        t0 = time.perf_counter()
+        prefill_oracle(q, k, v, k_pool, v_pool, table, torch.tensor([hist], dtype=torch.int32))
+        spent += time.perf_counter() - t0
+        flops += 4 * hq * d * (n * hist + n * (n + 1) // 2)
+        reps += 1
+    return flops, spent, f"{reps} x (1 sequence, {n} new tokens, history {hist})"
+
+
+def cpu_fill_sample(cfg, budget_s, seed=0):
+    from oracle import fill_kv_pages_oracle
+
+    tpp, d, hkv = cfg["tpp"], cfg["d"], cfg["hkv"]
+    T, P = 4096, 4096
+    g = torch.Generator().manual_seed(seed)
+    keys = torch.randn((T, hkv, d), generator=g).to(torch.bfloat16)
+    vals = torch.randn((T, hkv, d), generator=g).to(torch.bfloat16)
+    slots = torch.randperm(P * tpp, generator=g)[:T]
+    k_pool = torch.zeros((P, hkv, d // 8, tpp, 8), dtype=torch.bfloat16)
+    v_pool = torch.zeros((P, hkv, d, tpp), dtype=torch.bfloat16)
+    nbytes, spent, reps = 0, 0.0, 0
+    while spent < budget_s:
+        t0 = time.perf_counter()
+        fill_kv_pages_oracle(keys, vals, k_pool, v_pool, slots)
+        spent += time.perf_counter() - t0
+        nbytes += 4 * T * hkv * d * 2 + 8 * T
+        reps += 1
+    return nbytes, spent, f"{reps} x ({T} tokens into a {P}-page pool, pool clone included as in the reference)"
+
+
+def metric_of(kind):
+    return {"decode": ("paged decode KV GB/s", "GB/s"), "prefill": ("prefill TFLOPS", "TFLOP/s"), "fill": ("fill_kv_pages payload GB/s", "GB/s")}[kind]
+
+
+def cpu_measure(cfg, budget_s):
+    kind = cfg["kind"]
+    if kind == "decode":
+        nbytes, spent, nseq = cpu_decode_sample(cfg, budget_s)
+        return nbytes / spent / 1e9, f"first {nseq} sequences of the batch ({nbytes / 1e9:.3f} GB of KV)"
+    if kind == "prefill":
+        flops, spent, what = cpu_prefill_sample(cfg, budget_s)
+        return flops / spent / 1e12, what
+    nbytes, spent, what = cpu_fill_sample(cfg, budget_s)
+    return nbytes / spent / 1e9, what
+
+
+def run_reference(args, cfg, rank):
+    """The reference arm: the CPU oracle on all host threads, rank 0 only."""
+    if rank != 0:
+        return
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    metric, unit = metric_of(cfg["kind"])
+    per_step_budget = max(0.2, min(3.0, 150.0 / max(args.steps + args.warmup, 1)))
+    for _ in range(args.warmup):
+        cpu_measure(cfg, per_step_budget / 4)
+    vals, what, t0 = [], "", time.perf_counter()
+    for _ in range(args.steps):
+        v, what = cpu_measure(cfg, per_step_budget)
+        vals.append(v)
+    wall = time.perf_counter() - t0
+    value = sum(vals) / len(vals)
+    line = {"impl": "reference", "metric": metric, "value": value, "unit": unit, "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": wall / args.steps * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16 storage, f32 arithmetic",
+            "data": "synthetic", "config": {"workload": cfg["desc"]},
+            "cpu_baseline": {"value": value, "unit": unit, "cores": torch.get_num_threads(), "kind": "port", "sample": f"each step: {what}"},
+            "e2e": {"value": value, "unit": unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}, "gpu_launches": 0}
+    print(json.dumps(line), flush=True)
+
+
+# ------------------------------------------------------------------------------------------------
+# GPU side
+# ------------------------------------------------------------------------------------------------
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=2000)
+    ap.add_argument("--warmup", type=int, default=10)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="decode_8b", choices=sorted(WORKLOADS))
+    ap.add_argument("--prefill-impl", default="auto")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    cfg = WORKLOADS[args.workload]
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.impl == "reference":
+        run_reference(args, cfg, rank)
+        return
+
+    import torch.distributed as dist
+
+    import proxy_attention_lab_b200 as pal  # raises if the CUDA library is missing: no fallback
+
+    if not torch.cuda.is_available():
+        raise RuntimeError("bench.py needs a CUDA device; there is no CPU path")
+    device = torch.device("cuda", local_rank)
+    torch.cuda.set_device(device)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    kind = cfg["kind"]
+    metric, unit = metric_of(kind)
+    peaks = measured_peaks()
+    scaling = "weak"
+    extra_cfg = {}
+    if kind == "decode":
+        hkv_local = None
+        if args.workload == "decode_70b" and world > 1:
+            # total work fixed: each GPU owns Hkv/N kv heads (and their query heads) of every sequence
+            hkv_local, scaling = cfg["hkv"] // world, "strong"
+            extra_cfg["parallelism"] = f"kv-head sharded x{world}, no collective"
+        elif world > 1:
+            extra_cfg["parallelism"] = f"sequence sharded x{world} (each GPU its own batch of {cfg['S']}), no collective"
+        data = build_decode(cfg, device, seed=rank if hkv_local is None else 0, hkv_local=hkv_local)
+        pp = cfg["partition_pages"]
+
+        def step():
+            return pal.paged_attention_decode(data["q"], data["k_pool"], data["v_pool"], data["table"], data["lens"], partition_pages=pp)
+
+        q_dev, t_dev, l_dev = torch.empty_like(data["q"]), torch.empty_like(data["table"]), torch.empty_like(data["lens"])
+        out_host = torch.empty((cfg["S"], data["hq"], cfg["d"]), dtype=torch.bfloat16).pin_memory()
+
+        def e2e_step():
+            q_dev.copy_(data["q_host"], non_blocking=True)
+            t_dev.copy_(data["table_host"], non_blocking=True)
+            l_dev.copy_(data["lens_host"], non_blocking=True)
+            out = pal.paged_attention_decode(q_dev, data["k_pool"], data["v_pool"], t_dev, l_dev, partition_pages=pp)
+            out_host.copy_(out, non_blocking=True)
+
+        h2d = data["q_host"].numel() * 2 + data["table_host"].numel() * 4 + data["lens_host"].numel() * 4
+        d2h = out_host.numel() * 2
+        units_per_step, alg_per_step = data["kv_bytes"], data["alg_bytes"]
+        to_value = lambda units, sec: units / sec / 1e9
+        launches_per_step = 2 if pp else 1
+        bound, peak = "hbm", peaks["hbm"]
+        achieved_of = lambda sec: alg_per_step / sec / 1e9
+        roof_unit = "GB/s"
+        l2_note = "KV pool per GPU is larger than L2 (126 MB); every step streams it from HBM"
+    elif kind == "prefill":
+        seqs = None
+        if world > 1:
+            per = max(cfg["S"] // world, 1)
+            seqs = list(range(rank * per, min((rank + 1) * per, cfg["S"]))) or [rank % cfg["S"]]
+            scaling = "strong"
+            extra_cfg["parallelism"] = f"sequence sharded x{world}, no collective"
+        data = build_prefill(cfg, device, seed=0, seqs=seqs)
+
+        def step():
+            return pal.paged_attention_prefill(data["q"], data["k"], data["v"], data["k_pool"], data["v_pool"], data["table"], data["hist"],
+                                               impl=args.prefill_impl)
+
+        host = {k: data[k].cpu().pin_memory() for k in ("q", "k", "v", "table", "hist")}
+        devb = {k: torch.empty_like(data[k]) for k in host}
+        out_host = torch.empty((data["tokens"] * cfg["hq"], cfg["d"]), dtype=torch.bfloat16).pin_memory()
+
+        def e2e_step():
+            for k in host:
+                devb[k].copy_(host[k], non_blocking=True)
+            out = pal.paged_attention_prefill(devb["q"], devb["k"], devb["v"], data["k_pool"], data["v_pool"], devb["table"], devb["hist"],
+                                              impl=args.prefill_impl)
+            out_host.copy_(out, non_blocking=True)
+
+        h2d = sum(t.numel() * t.element_size() for t in host.values())
+        d2h = out_host.numel() * 2
+        units_per_step = alg_per_step = data["flops"]
+        to_value = lambda units, sec: units / sec / 1e12
+        launches_per_step = 1
+        bound, peak = "tensor", peaks["tensor_sustained"] if args.steps >= 200 else peaks["tensor"]
+        achieved_of = lambda sec: alg_per_step / sec / 1e12
+        roof_unit = "TFLOP/s"
+        l2_note = "L2 flushed by design of the workload: Q/K/V/out of a step total ~0.4 GB (> 126 MB L2)"
+    else:
+        data = build_fill(cfg, device, seed=rank)
+
+        def step():
+            return pal.fill_kv_pages(data["keys"], data["vals"], data["k_pool"], data["v_pool"], data["slots"])
+
+        kd, vd, sd = torch.empty_like(data["keys"]), torch.empty_like(data["vals"]), torch.empty_like(data["slots"])
+
+        def e2e_step():
+            kd.copy_(data["keys_host"], non_blocking=True)
+            vd.copy_(data["vals_host"], non_blocking=True)
+            sd.copy_(data["slots_host"], non_blocking=True)
+            pal.fill_kv_pages(kd, vd, data["k_pool"], data["v_pool"], sd)
+
+        h2d = data["keys_host"].numel() * 4 + data["slots_host"].numel() * 8
+        d2h = 0
+        units_per_step = alg_per_step = data["alg_bytes"]
+        to_value = lambda units, sec: units / sec / 1e9
+        launches_per_step = 1
+        bound, peak = "hbm", peaks["hbm"]
+        achieved_of = lambda sec: alg_per_step / sec / 1e9
+        roof_unit = "GB/s"
+        l2_note = "source tokens plus touched sectors exceed L2 (126 MB)"
+
+    def timed(fn, steps, warmup, sample_clocks):
+        for _ in range(warmup):
+            fn()
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        sampler = ClockSampler(local_rank) if sample_clocks else None
+        if sampler:
+            sampler.__enter__()
+        e0.record()
+        for _ in range(steps):
+            fn()
+        e1.record()
+        barrier()
+        if sampler:
+            sampler.__exit__()
+        ms = e0.elapsed_time(e1)
+        if world > 1:
+            t = torch.tensor([ms], device=device, dtype=torch.float64)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        return ms / 1e3, sampler
+
+    # quick self-check of the first result against the oracle on one sequence (decode only; cheap)
+    sec, sampler = timed(step, args.steps, args.warmup, True)
+    e2e_steps = max(3, min(args.steps, 200))
+    sec_e2e, _ = timed(e2e_step, e2e_steps, 3, False)
+
+    total_units, total_tokens = units_per_step, data["tokens"]
+    if world > 1:
+        kv_head_sharded = args.workload == "decode_70b"
+        t = torch.tensor([float(units_per_step), 0.0 if kv_head_sharded else float(data["tokens"])], device=device, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.SUM)
+        total_units = float(t[0].item())
+        total_tokens = data["tokens"] if kv_head_sharded else float(t[1].item())
+    per_step = sec / args.steps
+    value = to_value(total_units * args.steps, sec)
+    e2e_value = to_value(total_units * e2e_steps, sec_e2e)
+
+    if rank == 0:
+        achieved = achieved_of(per_step)
+        traffic = None
+        line = {
+            "metric": metric, "value": value, "unit": unit, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": per_step * 1e3, "higher_is_better": True, "scaling": scaling, "vs_baseline": None,
+            "dtype": "bf16 (f32 accumulate)", "data": "synthetic",
+            "config": {"workload": cfg["desc"], "l2": l2_note, **extra_cfg},
+            "tokens_per_s": total_tokens / per_step,
+            "e2e": {"value": e2e_value, "unit": unit, "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h), "steps": e2e_steps},
+            "gpu_launches": launches_per_step * args.steps,
+            "clocks": sampler.summary() if sampler else None,
+            "roofline": {"bound": bound, "achieved": achieved, "peak": peak, "unit": roof_unit, "frac": achieved / peak, "traffic": traffic,
+                         "peak_source": peaks["source"], "kernel": "rank 0 per-step time over the timed region (CUDA events)"},
+        }
+        if world == 1 and not args.no_cpu_baseline:
+            cores = os.cpu_count() or 1
+            torch.set_num_threads(cores)
+            v, what = cpu_measure(cfg, 12.0)
+            line["cpu_baseline"] = {"value": v, "unit": unit, "cores": torch.get_num_threads(), "kind": "port", "sample": what}
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()
