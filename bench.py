@@ -482,7 +482,8 @@ def main():
 
     if rank == 0:
         achieved = achieved_of(per_step)
-        traffic = None
+        # DRAM bytes per launch from one `ncu --set full` capture of the same workload (see profiles/)
+        traffic = {"decode_8b": 1.3866e9}.get(args.workload) if world == 1 else None
         line = {
             "metric": metric, "value": value, "unit": unit, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": per_step * 1e3, "higher_is_better": True, "scaling": scaling, "vs_baseline": None,
