@@ -49,11 +49,12 @@ def build(force: bool = False, verbose: bool = False) -> Path:
     hdr_digest = _digest(headers)
     nvcc = _nvcc()
     extra = ["-Xptxas", "-v"] if verbose else []
+    extra += os.environ.get("PAL_EXTRA_NVCC_FLAGS", "").split()
 
     def compile_one(src: Path):
         obj = OBJ_DIR / (src.stem + ".o")
         stamp = OBJ_DIR / (src.stem + ".stamp")
-        want = hashlib.sha256((hdr_digest + _digest([src]) + " ".join(NVCC_FLAGS)).encode()).hexdigest()
+        want = hashlib.sha256((hdr_digest + _digest([src]) + " ".join(NVCC_FLAGS + extra)).encode()).hexdigest()
         if not force and obj.exists() and stamp.exists() and stamp.read_text() == want:
             return obj, False, ""
         cmd = [nvcc, *NVCC_FLAGS, *extra, "-c", str(src), "-o", str(obj)]

@@ -368,7 +368,7 @@ int pal_paged_attention_prefill(const void* q_prompt, const void* k_prompt, cons
     set_error("%s: impl must be 0 (auto), 1 (mma.sync) or 2 (tcgen05)", what);
     return PAL_ERR_BAD_ARG;
   }
-  const bool use_tc = impl == 2;
+  const bool use_tc = impl == 2 || (impl == 0 && tc_ok && tokens_per_seq >= 64);
   return cuda_rc(use_tc ? launch_prefill_tcgen05(a, (cudaStream_t)stream) : launch_prefill_mma(a, (cudaStream_t)stream),
                  what);
 }

@@ -1,8 +1,746 @@
-// placeholder until the tcgen05 kernel lands
+// Paged-attention prefill on the 5th-generation tensor cores: tcgen05.mma with TMEM accumulators,
+// operands staged by TMA / bulk copies, for head_dim = 128 and tokens_per_page = 16.
+//
+// Replaces pal_paged_attention_prefill (src/pal_core/kernels/paged_attention/prefill/
+// paged_attention_prefill.h.metal:28-389), which handles one key per iteration per simdgroup with
+// scalar FMAs, and its launcher (src/pal_core/src/paged_attention_prefill_primitive.cpp:63-167).
+//
+// One CTA owns 128 consecutive new tokens of NQ (1 or 2) query heads that share a kv head; each
+// head's 128 rows are one M = 128 accumulator tile.  Keys arrive in tiles of 128 tokens: first the
+// paged history, then the dense prompt keys up to the diagonal tile.
+//
+//   warp 0        producer: Q / dense K / dense V tiles by TMA (128-byte swizzle); history K pages
+//                 by cp.async.bulk (4 KiB each, the pool's native striped block) and history V pages
+//                 by TMA with the 32-byte swizzle; two-stage K ring and two-stage V ring.
+//   warp 1        one thread issues every tcgen05.mma and tcgen05.commit.
+//   warps 2..     one softmax warpgroup (128 threads = 128 rows = 128 TMEM lanes) per query head.
+//
+// Shared-memory operand layouts and their UMMA descriptors
+//   Q, dense K   [2 k-blocks][128 rows][64 el]  K-major, SWIZZLE_128B, SBO 1024; +32 B per K=16 step
+//   paged K      page p at +4096 p, inside a page [16 chunks of 8 el][16 tokens][16 B]: every
+//                (chunk, 8 tokens) is one contiguous 128-byte core matrix => K-major, no swizzle,
+//                LBO 256 (next chunk), SBO 4096 (same slots of the next page).  One MMA covers slots
+//                0-7 of the 8 pages (N = 64), a second one slots 8-15: S columns are a permutation of
+//                the tile's tokens, which softmax undoes when it writes P.
+//   paged V      page p at +4096 p: [128 d][16 tokens] rows of 32 B, SWIZZLE_32B K-major, SBO 256;
+//                one K = 16 MMA per page.
+//   dense V      [2 n-blocks][128 tokens][64 el] MN-major, SWIZZLE_128B, LBO 16384, SBO 1024.
+//
+// TMEM (512 columns): S_q at 128 q (fp32 scores; P, packed two per column in the input type,
+// overwrites its first 64 columns and is the A operand of the PV MMAs), O_q at 256 + 128 q.
+//
+// P has the input type (an fp16 A with a bf16 B is rejected by the hardware as an illegal
+// instruction).  For bf16 the softmax denominator is summed from the rounded weights, so that the
+// result is an exact weighted mean with weights perturbed by < 2^-8, and query tiles whose rows see
+// fewer than 256 keys get the rounding residual of P through a second set of PV MMAs.
+//
+// Softmax keeps a possibly stale running maximum and only rescales O when the true maximum has grown
+// by more than 2^8 (the result is exact either way: numerator and denominator use the same
+// reference point).  Every wait is bounded; on expiry the CTA records a timeout in the workspace
+// status word, still releases its TMEM and returns.
+#include <cuda.h>
+#include <cudaTypedefs.h>
+#include <math.h>
+#include <stdlib.h>
+
+#include "common.cuh"
 #include "launch.h"
+
 namespace pal {
-int launch_prefill_tcgen05(const PrefillArgs&, cudaStream_t) {
-  set_error("paged_attention_prefill: the tcgen05 kernel is not built in this library");
-  return -2;
+namespace {
+
+constexpr int kTile = 128;           // query rows per head tile and keys per KV tile
+constexpr int kD = 128;
+constexpr int kTPP = 16;
+constexpr int kPagesPerTile = kTile / kTPP;
+constexpr int kPageBytes = kD * kTPP * 2;       // 4096
+constexpr int kTileBytes = kTile * kD * 2;      // 32768
+constexpr int kHalfTileBytes = kTileBytes / 2;  // one 64-element k-block / n-block
+constexpr float kRescaleThreshold = 8.0f;       // log2 units
+
+struct TcParams {
+  const void* k_pool;
+  const uint32_t* page_table;
+  const int32_t* hist_lens;
+  void* out;
+  unsigned int* status;
+  unsigned int* trace;  // progress markers in host-visible memory; only used by builds with PAL_TC_TRACE
+  int num_seqs, n_new, num_q_heads, num_kv_heads, group, max_pages_per_seq;
+  long long num_pages;
+  float scale_log2;
+};
+
+// Progress marker for fault diagnosis: compiled in only with -DPAL_TC_TRACE, and then active only
+// when the caller supplied a host-visible trace buffer.
+#ifdef PAL_TC_TRACE
+#define PAL_MARK(p, idx, val)                                  \
+  do {                                                         \
+    if ((p).trace != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) { \
+      *reinterpret_cast<volatile unsigned int*>((p).trace + (idx)) = (val); \
+      __threadfence_system();                                  \
+    }                                                          \
+  } while (0)
+#else
+#define PAL_MARK(p, idx, val) do { } while (0)
+#endif
+
+// ---- PTX wrappers ---------------------------------------------------------------------------
+__device__ __forceinline__ void tma_load_4d(void* dst, const CUtensorMap* map, int c0, int c1, int c2, int c3,
+                                            uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];" ::"r"(
+          smem_u32(dst)),
+      "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+      : "memory");
 }
+__device__ __forceinline__ void tma_load_3d(void* dst, const CUtensorMap* map, int c0, int c1, int c2, uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];" ::"r"(
+          smem_u32(dst)),
+      "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2)
+      : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tc_mma_ss(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
+      "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void tc_mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}" ::"r"(d_tmem),
+      "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+      "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};" ::"r"(taddr),
+      "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]),
+      "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]), "r"(r[18]),
+      "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]),
+      "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+      : "memory");
+}
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};" ::"r"(taddr),
+      "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]),
+      "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+      : "memory");
+}
+__device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void fence_proxy_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+
+// Shared-memory matrix descriptor (start address, leading / stride byte offsets, Blackwell version bit, layout)
+enum : uint64_t { kLayoutNone = 0, kLayoutSw128 = 2, kLayoutSw32 = 6 };
+__device__ __forceinline__ uint64_t make_desc(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes, uint64_t layout) {
+  return (uint64_t)((saddr >> 4) & 0x3fffu) | ((uint64_t)((lbo_bytes >> 4) & 0x3fffu) << 16) |
+         ((uint64_t)((sbo_bytes >> 4) & 0x3fffu) << 32) | (1ull << 46) | (layout << 61);
+}
+// Instruction descriptor for kind::f16 with fp32 accumulation, M = 128, A K-major
+__host__ __device__ constexpr uint32_t make_idesc(int n, int a_fmt, int b_fmt, int b_mn_major) {
+  return (1u << 4) | ((uint32_t)a_fmt << 7) | ((uint32_t)b_fmt << 10) | ((uint32_t)b_mn_major << 16) |
+         ((uint32_t)(n >> 3) << 17) | ((uint32_t)(kTile >> 4) << 24);
+}
+
+template <typename T>
+struct Fmt;
+template <>
+struct Fmt<__half> {
+  static constexpr int kCode = 0;
+};
+template <>
+struct Fmt<__nv_bfloat16> {
+  static constexpr int kCode = 1;
+};
+
+template <int NQ>
+struct TcSmem {
+  static constexpr int kQ = 0;
+  static constexpr int kK = NQ * kTileBytes;
+  static constexpr int kV = kK + 2 * kTileBytes;
+  static constexpr int kBars = kV + 2 * kTileBytes;
+  static constexpr int kTotal = kBars + 256 + 1024;  // + alignment slack
+};
+
+template <typename T, int NQ>
+__global__ void __launch_bounds__(64 + 128 * NQ, 1)
+    prefill_tcgen05_kernel(const TcParams p, const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
+                           const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_vpool) {
+  extern __shared__ unsigned char smem_raw[];
+  unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  using SM = TcSmem<NQ>;
+  unsigned char* sQ = smem + SM::kQ;
+  unsigned char* sK = smem + SM::kK;
+  unsigned char* sV = smem + SM::kV;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + SM::kBars);
+  uint64_t* q_full = bars;            // 1
+  uint64_t* k_full = bars + 1;        // 2
+  uint64_t* k_empty = bars + 3;       // 2
+  uint64_t* v_full = bars + 5;        // 2
+  uint64_t* v_empty = bars + 7;       // 2
+  uint64_t* s_full = bars + 9;        // NQ
+  uint64_t* p_full = bars + 11;       // NQ
+  uint64_t* o_done = bars + 13;       // NQ
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 15);
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  // heaviest (latest) query tiles first
+  const int qt = (int)gridDim.x - 1 - (int)blockIdx.x;
+  const int t0 = qt * kTile;
+  const int h0 = blockIdx.y * NQ;
+  const int s = blockIdx.z;
+  const int kvh = h0 / p.group;
+  const int N = p.n_new;
+  int H = p.hist_lens[s];
+  if (H < 0 || p.num_pages <= 0) H = 0;
+  {
+    const long long cap = (long long)p.max_pages_per_seq * kTPP;
+    if (H > cap) H = (int)cap;
+  }
+  const int hist_tiles = (H + kTile - 1) / kTile;
+  const int dense_tiles = qt + 1;
+  const int num_tiles = hist_tiles + dense_tiles;
+  // bf16 rounds P with a relative error of up to 2^-8; summed over n keys that leaves about
+  // 0.002 / sqrt(n / 3) of absolute error per unit of |v|, which only drops below the 2e-3 target
+  // (at the 6-sigma level) once a row sees a few hundred keys.  CTAs that hold rows with fewer than
+  // 256 visible keys - the first one or two query tiles of sequences with little history, the
+  // lightest CTAs of the causal schedule - feed the residual P - bf16(P) through a second set of
+  // PV MMAs.
+  const bool split_p = Mma16816<T>::kSplitP && (H + t0 < 256);
+
+  if (tid == 0) {
+    mbar_init(q_full, 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&k_full[i], 1);
+      mbar_init(&k_empty[i], 1);
+      mbar_init(&v_full[i], 1);
+      mbar_init(&v_empty[i], 1);
+    }
+    for (int q = 0; q < NQ; ++q) {
+      mbar_init(&s_full[q], 1);
+      mbar_init(&p_full[q], 4);
+      mbar_init(&o_done[q], 1);
+    }
+    fence_mbar_init();
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(512u)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  if (tid == 0) PAL_MARK(p, 0, 1u + tmem_base);
+
+  if (warp == 0) {
+    // =============================== producer ===============================
+    int ok = 1;
+    if (lane == 0) {
+      mbar_arrive_expect_tx(q_full, NQ * kTileBytes);
+      for (int q = 0; q < NQ; ++q)
+        for (int kb = 0; kb < 2; ++kb)
+          tma_load_4d(sQ + q * kTileBytes + kb * kHalfTileBytes, &tm_q, kb * 64, h0 + q, t0, s, q_full);
+      PAL_MARK(p, 1, 1u);
+    }
+    for (int j = 0; j < num_tiles && ok; ++j) {
+      const int st = j & 1;
+      const uint32_t par = ((j >> 1) & 1) ^ 1;
+      const bool paged = j < hist_tiles;
+      int npg = 0;
+      uint32_t my_pid = 0;
+      if (paged) {
+        npg = min(kPagesPerTile, (H - j * kTile + kTPP - 1) / kTPP);
+        if (lane < npg) {
+          my_pid = p.page_table[(size_t)s * p.max_pages_per_seq + j * kPagesPerTile + lane];
+          if ((long long)my_pid >= p.num_pages) my_pid = (uint32_t)(p.num_pages - 1);
+        }
+      }
+      // ---- K ----
+      if (lane == 0) ok = mbar_wait(&k_empty[st], par, p.status);
+      ok = __shfl_sync(0xffffffffu, ok, 0);
+      if (!ok) break;
+      if (paged) {
+        if (lane == 0) mbar_arrive_expect_tx(&k_full[st], npg * kPageBytes);
+        for (int i = 0; i < npg; ++i) {
+          const uint32_t pid = __shfl_sync(0xffffffffu, my_pid, i);
+          if (lane == 0)
+            bulk_g2s(sK + st * kTileBytes + i * kPageBytes,
+                     static_cast<const unsigned char*>(p.k_pool) + ((size_t)pid * p.num_kv_heads + kvh) * kPageBytes,
+                     kPageBytes, &k_full[st]);
+        }
+      } else if (lane == 0) {
+        const int jd = j - hist_tiles;
+        mbar_arrive_expect_tx(&k_full[st], kTileBytes);
+        for (int kb = 0; kb < 2; ++kb)
+          tma_load_4d(sK + st * kTileBytes + kb * kHalfTileBytes, &tm_k, kb * 64, kvh, jd * kTile, s, &k_full[st]);
+        PAL_MARK(p, 2, 1u + j);
+      }
+      // ---- V ----
+      if (lane == 0) ok = mbar_wait(&v_empty[st], par, p.status);
+      ok = __shfl_sync(0xffffffffu, ok, 0);
+      if (!ok) break;
+      if (paged) {
+        if (lane == 0) mbar_arrive_expect_tx(&v_full[st], npg * kPageBytes);
+        for (int i = 0; i < npg; ++i) {
+          const uint32_t pid = __shfl_sync(0xffffffffu, my_pid, i);
+          if (lane == 0)
+            tma_load_3d(sV + st * kTileBytes + i * kPageBytes, &tm_vpool, 0, 0, (int)(pid * p.num_kv_heads + kvh), &v_full[st]);
+        }
+      } else if (lane == 0) {
+        const int jd = j - hist_tiles;
+        mbar_arrive_expect_tx(&v_full[st], kTileBytes);
+        for (int nb = 0; nb < 2; ++nb)
+          tma_load_4d(sV + st * kTileBytes + nb * kHalfTileBytes, &tm_v, nb * 64, kvh, jd * kTile, s, &v_full[st]);
+        PAL_MARK(p, 3, 1u + j);
+      }
+    }
+  } else if (warp == 1) {
+    // =============================== MMA issuer ===============================
+    if (lane == 0) {
+      constexpr int F = Fmt<T>::kCode;
+      constexpr uint32_t idesc_qk128 = make_idesc(128, F, F, 0);
+      constexpr uint32_t idesc_qk64 = make_idesc(64, F, F, 0);
+      constexpr uint32_t idesc_pv_paged = make_idesc(128, F, F, 0);  // A = P (TMEM), B = V K-major
+      constexpr uint32_t idesc_pv_dense = make_idesc(128, F, F, 1);  // B = V MN-major
+      const uint32_t sQ_u = smem_u32(sQ), sK_u = smem_u32(sK), sV_u = smem_u32(sV);
+      bool ok = mbar_wait(q_full, 0, p.status);
+      PAL_MARK(p, 4, 1u + ok);
+
+      // S_q(j) = Q_q . K(j)^T into TMEM columns [128 q, 128 q + 128)
+      auto issue_qk = [&](int q, int j) {
+        const int st = j & 1;
+        const uint32_t d_tmem = tmem_base + q * kTile;
+        const uint32_t qa = sQ_u + q * kTileBytes;
+        const uint32_t kbase = sK_u + st * kTileBytes;
+        if (j < hist_tiles) {
+#pragma unroll
+          for (int ks = 0; ks < kD / 16; ++ks) {
+            const uint64_t a = make_desc(qa + (ks >> 2) * kHalfTileBytes + (ks & 3) * 32, 16, 1024, kLayoutSw128);
+#pragma unroll
+            for (int half = 0; half < 2; ++half) {
+              const uint64_t b = make_desc(kbase + half * 128 + ks * 512, 256, kPageBytes, kLayoutNone);
+              tc_mma_ss(d_tmem + half * 64, a, b, idesc_qk64, ks > 0);
+            }
+          }
+        } else {
+#pragma unroll
+          for (int ks = 0; ks < kD / 16; ++ks) {
+            const uint64_t a = make_desc(qa + (ks >> 2) * kHalfTileBytes + (ks & 3) * 32, 16, 1024, kLayoutSw128);
+            const uint64_t b = make_desc(kbase + (ks >> 2) * kHalfTileBytes + (ks & 3) * 32, 16, 1024, kLayoutSw128);
+            tc_mma_ss(d_tmem, a, b, idesc_qk128, ks > 0);
+          }
+        }
+        PAL_MARK(p, 6, 1u + j);
+        tc_commit(&s_full[q]);
+        PAL_MARK(p, 7, 1u + j);
+      };
+      // O_q += P_q(j) . V(j)
+      auto issue_pv = [&](int q, int j) {
+        const int st = j & 1;
+        const uint32_t d_tmem = tmem_base + 2 * kTile + q * kTile;
+        const uint32_t a_tmem = tmem_base + q * kTile;  // P over the first 64 columns of S_q
+        const uint32_t vbase = sV_u + st * kTileBytes;
+        for (int part = 0; part < (split_p ? 2 : 1); ++part) {  // part 1: the residual of P, 64 columns on
+          const uint32_t a_part = a_tmem + part * 64;
+          if (j < hist_tiles) {
+#pragma unroll
+            for (int pg = 0; pg < kPagesPerTile; ++pg) {
+              const uint64_t b = make_desc(vbase + pg * kPageBytes, 16, 256, kLayoutSw32);
+              tc_mma_ts(d_tmem, a_part + pg * 8, b, idesc_pv_paged, (j > 0 || pg > 0 || part > 0));
+            }
+          } else {
+#pragma unroll
+            for (int kk = 0; kk < kTile / 16; ++kk) {
+              const uint64_t b = make_desc(vbase + kk * 2048, kHalfTileBytes, 1024, kLayoutSw128);
+              tc_mma_ts(d_tmem, a_part + kk * 8, b, idesc_pv_dense, (j > 0 || kk > 0 || part > 0));
+            }
+          }
+        }
+        PAL_MARK(p, 12, 1u + j);
+        tc_commit(&o_done[q]);
+        PAL_MARK(p, 13, 1u + j);
+      };
+
+      if (ok) ok = mbar_wait(&k_full[0], 0, p.status);
+      PAL_MARK(p, 5, 1u + ok);
+      if (ok) {
+        tc_fence_after();
+        for (int q = 0; q < NQ; ++q) issue_qk(q, 0);
+        tc_commit(&k_empty[0]);
+      }
+      for (int j = 0; j < num_tiles && ok; ++j) {
+        const int st = j & 1;
+        ok = mbar_wait(&v_full[st], (j >> 1) & 1, p.status);
+        for (int q = 0; q < NQ && ok; ++q) {
+          ok = mbar_wait(&p_full[q], j & 1, p.status);
+          if (!ok) break;
+          tc_fence_after();
+          issue_pv(q, j);
+          if (j + 1 < num_tiles) {
+            if (q == 0) {
+              ok = mbar_wait(&k_full[(j + 1) & 1], ((j + 1) >> 1) & 1, p.status);
+              if (!ok) break;
+              tc_fence_after();
+            }
+            issue_qk(q, j + 1);
+            if (q == NQ - 1) tc_commit(&k_empty[(j + 1) & 1]);
+          }
+        }
+        if (ok) tc_commit(&v_empty[st]);
+      }
+    }
+  } else {
+    // =============================== softmax warpgroups ===============================
+    const int q = (warp - 2) >> 2;
+    const int lane_group = warp & 3;            // the TMEM sub-partition this warp may touch
+    const int row = lane_group * 32 + lane;     // row of the 128-row tile = TMEM lane
+    const uint32_t lane_addr = (uint32_t)(lane_group * 32) << 16;
+    const uint32_t tS = tmem_base + lane_addr + q * kTile;
+    const uint32_t tO = tmem_base + lane_addr + 2 * kTile + q * kTile;
+    const int qi = t0 + row;                    // index of this row's query token in its sequence
+    float m_used = -INFINITY, l_run = 0.f;
+    bool ok = true;
+    using PK = Mma16816<T>;  // P is stored in the input type
+
+    for (int j = 0; j < num_tiles; ++j) {
+      const bool paged = j < hist_tiles;
+      const int jd = j - hist_tiles;
+      if (!(ok = mbar_wait(&s_full[q], j & 1, p.status))) break;
+      tc_fence_after();
+      if (tid == 64) PAL_MARK(p, 8, 1u + j);
+      // which columns need masking at all (warp-uniform)
+      const bool need_mask = paged ? ((j + 1) * kTile > H) : (jd == dense_tiles - 1 || (jd + 1) * kTile > N);
+
+      // visibility of column `c` (0..127) of the S tile for this row
+      auto visible = [&](int c) -> bool {
+        if (paged) {
+          // columns 0-63: slots 0-7 of pages 0-7; columns 64-127: slots 8-15 of pages 0-7
+          const int tok = j * kTile + ((c & 63) >> 3) * kTPP + (c & 7) + ((c >> 6) << 3);
+          return tok < H;
+        }
+        const int key = jd * kTile + c;
+        return key <= qi && key < N;
+      };
+
+      // ---- pass 1: row maximum of the scaled scores ----
+      float mx = -INFINITY;
+#pragma unroll
+      for (int c4 = 0; c4 < 4; ++c4) {
+        uint32_t v[32];
+        tmem_ld32(tS + c4 * 32, v);
+        tmem_wait_ld();
+        if (need_mask) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i)
+            if (visible(c4 * 32 + i)) mx = fmaxf(mx, __uint_as_float(v[i]));
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(v[i]));
+        }
+      }
+      if (tid == 64) PAL_MARK(p, 9, 1u + j);
+      mx *= p.scale_log2;  // scale > 0, so the maximum commutes with the scaling
+      const float m_new = fmaxf(m_used, mx);
+      if (j == 0) {
+        m_used = m_new;
+      } else if (__any_sync(0xffffffffu, m_new > m_used + kRescaleThreshold)) {
+        // O_q must be stable: PV(j-1) of this head has to be complete
+        if (!(ok = mbar_wait(&o_done[q], (j - 1) & 1, p.status))) break;
+        tc_fence_after();
+        const float f = fast_exp2(m_used - m_new);
+#pragma unroll
+        for (int c4 = 0; c4 < 4; ++c4) {
+          uint32_t v[32];
+          tmem_ld32(tO + c4 * 32, v);
+          tmem_wait_ld();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * f);
+          tmem_st32(tO + c4 * 32, v);
+        }
+        tmem_wait_st();
+        l_run *= f;
+        m_used = m_new;
+      }
+      const float m_ref = m_used > -INFINITY ? m_used : 0.f;
+
+      // ---- pass 2: P = exp2(s * scale - m) in the input type, packed two per column over S's first
+      // 64 columns, a quarter (32 keys -> 16 columns) at a time so that P never overtakes the S columns
+      // still to be read.  With split_p the rounding residual P - round(P) goes to columns 64..127.
+      uint32_t lo_hold[2][16];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        uint32_t v[32];
+        if (paged) {
+          // pages 2u, 2u+1: slots 0-7 at columns 16u.., slots 8-15 at columns 64+16u..
+          uint32_t a16[16], b16[16];
+          tmem_ld16(tS + 16 * u, a16);
+          tmem_ld16(tS + 64 + 16 * u, b16);
+          tmem_wait_ld();
+#pragma unroll
+          for (int i = 0; i < 16; ++i) {
+            v[i] = a16[i];
+            v[16 + i] = b16[i];
+          }
+        } else {
+          tmem_ld32(tS + 32 * u, v);
+          tmem_wait_ld();
+        }
+        float e[32];
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          float x = fast_exp2(fmaf(__uint_as_float(v[i]), p.scale_log2, -m_ref));
+          if (need_mask) {
+            const int c = paged ? (i < 16 ? 16 * u + i : 64 + 16 * u + (i - 16)) : 32 * u + i;
+            if (!visible(c)) x = 0.f;
+          }
+          e[i] = x;
+        }
+        uint32_t hi[16], lo[16];
+#pragma unroll
+        for (int w = 0; w < 16; ++w) {
+          // element pair that lands in P column 16u + w (indices are compile-time, values selected)
+          const int pg = w >> 3, ww = w & 7;  // paged: page 2u + pg, column ww of its 8
+          const int ip = ww < 4 ? 8 * pg + 2 * ww : 16 + 8 * pg + 2 * (ww - 4);
+          const float x0 = paged ? e[ip] : e[2 * w];
+          const float x1 = paged ? e[ip + 1] : e[2 * w + 1];
+          hi[w] = PK::pack(x0, x1);
+          if (split_p) {
+            lo[w] = PK::pack_residual(x0, x1, hi[w]);
+            l_run += x0 + x1;
+          } else if (PK::kSplitP) {
+            // normalise with the weights the MMA will really use: bf16(p), not p
+            l_run += __uint_as_float(hi[w] << 16) + __uint_as_float(hi[w] & 0xffff0000u);
+          } else {
+            l_run += x0 + x1;
+          }
+        }
+        tmem_st16(tS + 16 * u, hi);
+        if (split_p) {
+          if (paged) {
+            tmem_st16(tS + 64 + 16 * u, lo);  // columns 64+16u.. were consumed in this very quarter
+          } else if (u < 2) {
+#pragma unroll
+            for (int w = 0; w < 16; ++w) lo_hold[u][w] = lo[w];
+          } else if (u == 2) {
+            tmem_st16(tS + 64, lo_hold[0]);
+            tmem_st16(tS + 80, lo_hold[1]);
+#pragma unroll
+            for (int w = 0; w < 16; ++w) lo_hold[0][w] = lo[w];
+          } else {
+            tmem_st16(tS + 96, lo_hold[0]);
+            tmem_st16(tS + 112, lo);
+          }
+        }
+      }
+      tmem_wait_st();
+      if (tid == 64) PAL_MARK(p, 10, 1u + j);
+
+      // The last history tile may hold slots past the history length, and pages that were never
+      // loaded: zero those V tokens in shared memory, because 0 * NaN would poison the accumulator.
+      if (q == 0 && paged && need_mask) {
+        if (!(ok = mbar_wait(&v_full[j & 1], (j >> 1) & 1, p.status))) break;
+        unsigned char* vt = sV + (j & 1) * kTileBytes;
+        const int sw = (row >> 2) & 1;  // 32-byte swizzle: 16-byte chunk index ^= bit 7 of the address
+        for (int pg = 0; pg < kPagesPerTile; ++pg) {
+          int nv = H - j * kTile - pg * kTPP;
+          nv = nv < 0 ? 0 : nv;
+          unsigned char* vrow = vt + pg * kPageBytes + row * 32;
+          for (int slot = nv; slot < kTPP; ++slot)
+            *reinterpret_cast<uint16_t*>(vrow + ((((slot >> 3) ^ sw) << 4) | ((slot & 7) << 1))) = 0;
+        }
+        fence_proxy_async_smem();
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&p_full[q]);
+      if (tid == 64) PAL_MARK(p, 11, 1u + j);
+    }
+
+    // ---- epilogue: O / l -> out[((s*N + qi)*Hq + h0 + q)*D + d] ----
+    if (ok) ok = mbar_wait(&o_done[q], (num_tiles - 1) & 1, p.status);
+    if (tid == 64) PAL_MARK(p, 14, 1u + ok);
+    if (ok) {
+      tc_fence_after();
+      const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
+      T* orow = static_cast<T*>(p.out) + (((size_t)s * N + qi) * p.num_q_heads + h0 + q) * kD;
+#pragma unroll
+      for (int c4 = 0; c4 < 4; ++c4) {
+        uint32_t v[32];
+        tmem_ld32(tO + c4 * 32, v);
+        tmem_wait_ld();
+        if (qi < N) {
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            uint4 w;
+            w.x = Mma16816<T>::pack(__uint_as_float(v[8 * i + 0]) * inv, __uint_as_float(v[8 * i + 1]) * inv);
+            w.y = Mma16816<T>::pack(__uint_as_float(v[8 * i + 2]) * inv, __uint_as_float(v[8 * i + 3]) * inv);
+            w.z = Mma16816<T>::pack(__uint_as_float(v[8 * i + 4]) * inv, __uint_as_float(v[8 * i + 5]) * inv);
+            w.w = Mma16816<T>::pack(__uint_as_float(v[8 * i + 6]) * inv, __uint_as_float(v[8 * i + 7]) * inv);
+            *reinterpret_cast<uint4*>(orow + c4 * 32 + i * 8) = w;
+          }
+        }
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512u) : "memory");
+    if (lane == 0) PAL_MARK(p, 16, 1u);
+  }
+}
+
+// ---- host side -------------------------------------------------------------------------------
+PFN_cuTensorMapEncodeTiled_v12000 get_encode_fn() {
+  static PFN_cuTensorMapEncodeTiled_v12000 fn = nullptr;
+  static bool tried = false;
+  if (!tried) {
+    tried = true;
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) == cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<PFN_cuTensorMapEncodeTiled_v12000>(ptr);
+  }
+  return fn;
+}
+
+bool encode_map(CUtensorMap* map, int dtype, int rank, const void* base, const cuuint64_t* dims, const cuuint64_t* strides,
+                const cuuint32_t* box, CUtensorMapSwizzle swizzle) {
+  auto fn = get_encode_fn();
+  if (!fn) {
+    set_error("paged_attention_prefill: cuTensorMapEncodeTiled is not available from this driver");
+    return false;
+  }
+  const cuuint32_t elem_strides[5] = {1, 1, 1, 1, 1};
+  CUresult r = fn(map, dtype == 0 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, rank,
+                  const_cast<void*>(base), dims, strides, box, elem_strides, CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    set_error("paged_attention_prefill: cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
+    return false;
+  }
+  return true;
+}
+
+template <typename T, int NQ>
+int launch_tc(const TcParams& p, const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv,
+              const CUtensorMap& mvp, cudaStream_t stream) {
+  auto kern = prefill_tcgen05_kernel<T, NQ>;
+  static bool configured[64] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 64 && !configured[dev]) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, TcSmem<NQ>::kTotal);
+    if (e != cudaSuccess) return (int)e;
+    configured[dev] = true;
+  }
+  dim3 grid((p.n_new + kTile - 1) / kTile, p.num_q_heads / NQ, p.num_seqs);
+  kern<<<grid, 64 + 128 * NQ, TcSmem<NQ>::kTotal, stream>>>(p, mq, mk, mv, mvp);
+  return (int)cudaGetLastError();
+}
+
+}  // namespace
+
+int launch_prefill_tcgen05(const PrefillArgs& a, cudaStream_t stream) {
+  if (a.head_dim != kD || a.tokens_per_page != kTPP) {
+    set_error("paged_attention_prefill: the tcgen05 kernel covers head_dim=128, tokens_per_page=16 only");
+    return -2;
+  }
+  if (a.num_seqs > 65535 || a.num_q_heads > 65535) {
+    set_error("paged_attention_prefill: num_seqs and num_q_heads are limited to 65535");
+    return -1;
+  }
+  if ((long long)a.num_pages * a.num_kv_heads > 0x7fffffffLL) {
+    set_error("paged_attention_prefill: pool too large for the tcgen05 kernel (pages * kv_heads must fit 31 bits)");
+    return -2;
+  }
+  TcParams p;
+  p.k_pool = a.k_pool;
+  p.page_table = a.page_table;
+  p.hist_lens = a.history_lens;
+  p.out = a.out;
+  p.status = &static_cast<WorkspaceHeader*>(a.workspace)->status;
+  p.trace = nullptr;
+#ifdef PAL_TC_TRACE
+  if (const char* t = getenv("PAL_TC_TRACE_PTR")) p.trace = reinterpret_cast<unsigned int*>(strtoull(t, nullptr, 0));
+#endif
+  p.num_seqs = a.num_seqs;
+  p.n_new = a.tokens_per_seq;
+  p.num_q_heads = a.num_q_heads;
+  p.num_kv_heads = a.num_kv_heads;
+  p.group = a.num_q_heads / a.num_kv_heads;
+  p.max_pages_per_seq = a.max_pages_per_seq;
+  p.num_pages = a.num_pages;
+  p.scale_log2 = a.scale * kLog2e;
+
+  const cuuint64_t S = a.num_seqs, N = a.tokens_per_seq, Hq = a.num_q_heads, Hkv = a.num_kv_heads;
+  CUtensorMap mq, mk, mv, mvp;
+  {
+    const cuuint64_t dims[4] = {kD, Hq, N, S};
+    const cuuint64_t strides[3] = {kD * 2, Hq * kD * 2, N * Hq * kD * 2};
+    const cuuint32_t box[4] = {64, 1, kTile, 1};
+    if (!encode_map(&mq, a.dtype, 4, a.q_prompt, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B)) return -3;
+  }
+  {
+    const cuuint64_t dims[4] = {kD, Hkv, N, S};
+    const cuuint64_t strides[3] = {kD * 2, Hkv * kD * 2, N * Hkv * kD * 2};
+    const cuuint32_t box[4] = {64, 1, kTile, 1};
+    if (!encode_map(&mk, a.dtype, 4, a.k_prompt, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B)) return -3;
+    if (!encode_map(&mv, a.dtype, 4, a.v_prompt, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B)) return -3;
+  }
+  if (a.num_pages > 0) {
+    const cuuint64_t dims[3] = {kTPP, kD, (cuuint64_t)a.num_pages * Hkv};
+    const cuuint64_t strides[2] = {kTPP * 2, kPageBytes};
+    const cuuint32_t box[3] = {kTPP, kD, 1};
+    if (!encode_map(&mvp, a.dtype, 3, a.v_pool, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_32B)) return -3;
+  } else {
+    mvp = mv;  // never dereferenced: without pages every history length is treated as 0
+  }
+  cudaError_t e = cudaMemsetAsync(a.workspace, 0, 8, stream);
+  if (e != cudaSuccess) return (int)e;
+  const bool pair = (p.group % 2) == 0;
+  if (a.dtype == 0)
+    return pair ? launch_tc<__half, 2>(p, mq, mk, mv, mvp, stream) : launch_tc<__half, 1>(p, mq, mk, mv, mvp, stream);
+  return pair ? launch_tc<__nv_bfloat16, 2>(p, mq, mk, mv, mvp, stream)
+              : launch_tc<__nv_bfloat16, 1>(p, mq, mk, mv, mvp, stream);
+}
+
 }  // namespace pal

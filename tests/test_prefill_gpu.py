@@ -18,6 +18,10 @@ def run_prefill(pal, case, device, **kw):
     return out.cpu()
 
 
+def supported(impl, d, tpp=16):
+    return impl == "mma" or (d == 128 and tpp == 16)
+
+
 def check(pal, cuda, case, impl, tol=TOL):
     ref = prefill_oracle(case.q, case.k_new, case.v_new, case.k_pool, case.v_pool, case.page_table, case.hist)
     out = run_prefill(pal, case, cuda, impl=impl)
@@ -32,7 +36,7 @@ def check(pal, cuda, case, impl, tol=TOL):
     assert not bad.any(), f"max-abs {diff.max().item()} with {int(bad.sum())} elements out of tolerance"
 
 
-IMPLS = ["mma"]
+IMPLS = ["mma", "tcgen05"]  # tcgen05 covers head_dim 128 / tokens_per_page 16
 
 
 @pytest.mark.parametrize("impl", IMPLS)
@@ -43,6 +47,8 @@ IMPLS = ["mma"]
 )
 def test_reference_shape_list(pal, cuda, impl, dtype, batch, hist, n, heads, d):
     """Shape list of tests/paged_attention/prefill/test_sdpa_equivalency.py:21-27."""
+    if not supported(impl, d):
+        pytest.skip("shape outside the tcgen05 kernel")
     case = make_prefill_case(5, [hist] * batch, n, heads[0], heads[1], d, dtype=dtype)
     check(pal, cuda, case, impl)
 
@@ -51,6 +57,8 @@ def test_reference_shape_list(pal, cuda, impl, dtype, batch, hist, n, heads, d):
 @pytest.mark.parametrize("d", [32, 64, 80, 96, 128, 256])
 @pytest.mark.parametrize("tpp", [16, 32])
 def test_head_dims_and_page_sizes(pal, cuda, impl, d, tpp):
+    if not supported(impl, d, tpp):
+        pytest.skip("shape outside the tcgen05 kernel")
     case = make_prefill_case(9, [0, 70, 129], 77, 4, 2, d, tpp=tpp, dtype=torch.bfloat16)
     check(pal, cuda, case, impl)
 
@@ -71,7 +79,7 @@ def test_llama8b_shape_reduced(pal, cuda, impl):
 @pytest.mark.parametrize("impl", IMPLS)
 def test_no_history_empty_pool(pal, cuda, impl):
     """tests/paged_attention/prefill/test_softmax_and_value.py:72-78: zero-page pools and an (S, 0) page table."""
-    dtype, d = torch.float16, 64
+    dtype, d = torch.float16, (64 if impl == "mma" else 128)
     q = torch.ones((1, 1, d), dtype=dtype, device=cuda)
     k = torch.ones((1, 1, d), dtype=dtype, device=cuda)
     v = torch.zeros((1, 1, d), dtype=dtype, device=cuda)
@@ -92,3 +100,26 @@ def test_determinism(pal, cuda, impl, n, hist):
     a = run_prefill(pal, case, cuda, impl=impl)
     b = run_prefill(pal, case, cuda, impl=impl)
     assert torch.equal(a, b)
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+def test_tcgen05_matches_mma(pal, cuda, dtype):
+    """The two implementations agree with each other (odd group size -> one head per CTA, ragged N)."""
+    case = make_prefill_case(33, [0, 500, 129], 200, 6, 2, 128, dtype=dtype)
+    a = run_prefill(pal, case, cuda, impl="mma")
+    b = run_prefill(pal, case, cuda, impl="tcgen05")
+    assert max_abs(a, b) <= 2 * TOL + 2.0 ** -7 * a.float().abs().max().item()
+    check(pal, cuda, case, "tcgen05")
+
+
+def test_tcgen05_unsupported_shape_raises(pal, cuda):
+    case = make_prefill_case(35, [10], 16, 4, 2, 64, dtype=torch.float16)
+    t = to_dev(case, cuda)
+    with pytest.raises(RuntimeError):
+        pal.paged_attention_prefill(t["q"], t["k_new"], t["v_new"], t["k_pool"], t["v_pool"], t["page_table"], t["hist"], impl="tcgen05")
+
+
+def test_chunked_prefill_config_reduced(pal, cuda):
+    """Llama-3-8B chunked causal prefill shape, 3 sequences x 2048 new tokens over ragged history (auto impl)."""
+    case = make_prefill_case(0, [0, 4096, 1111], 2048, 32, 8, 128, dtype=torch.bfloat16)
+    check(pal, cuda, case, "auto")
