@@ -1,0 +1,77 @@
+"""Host-side plumbing for running the operators on several GPUs of one node.
+
+The attention output of (sequence s, query head h) depends only on that sequence's pages of kv head
+``h // group``, so a batch shards by sequence and by kv head with no communication at all.  The one
+exchange step is the long-context layout in which every GPU holds a slice of each sequence's
+context: each rank produces un-normalised ``(m, l, acc)`` partials over its slice, the partials are
+all-gathered (NCCL over NVLink on GPUs) and merged by the log-sum-exp combine kernel.
+
+The reference has no multi-device code (it is a single-GPU MLX extension); this module has no
+counterpart there.
+"""
+
+from __future__ import annotations
+
+from typing import Callable, List, Sequence
+
+import torch
+import torch.distributed as dist
+
+
+def partition_sequences(lengths: Sequence[int], world_size: int) -> List[List[int]]:
+    """Greedy longest-first assignment of sequences to ranks, balancing the tokens each rank streams."""
+    order = sorted(range(len(lengths)), key=lambda i: (-int(lengths[i]), i))
+    loads = [0] * world_size
+    parts: List[List[int]] = [[] for _ in range(world_size)]
+    for i in order:
+        r = min(range(world_size), key=lambda j: (loads[j], j))
+        parts[r].append(i)
+        loads[r] += int(lengths[i])
+    for p in parts:
+        p.sort()
+    return parts
+
+
+def kv_head_range(num_kv_heads: int, world_size: int, rank: int) -> range:
+    """Contiguous kv heads owned by ``rank`` (the query heads ``h*group .. (h+1)*group-1`` go with them)."""
+    if num_kv_heads % world_size != 0:
+        raise ValueError(f"num_kv_heads ({num_kv_heads}) must be a multiple of the world size ({world_size})")
+    per = num_kv_heads // world_size
+    return range(rank * per, (rank + 1) * per)
+
+
+def context_slice(num_pages: int, world_size: int, rank: int) -> range:
+    """Logical pages of a sequence owned by ``rank`` when its context is cut into contiguous slices."""
+    per = (num_pages + world_size - 1) // world_size
+    lo = min(rank * per, num_pages)
+    return range(lo, min(lo + per, num_pages))
+
+
+def all_gather_partials(m: torch.Tensor, l: torch.Tensor, acc: torch.Tensor, group=None):
+    """All-gather one ``(m [R], l [R], acc [R, D])`` triple per rank into ``[world, ...]`` stacks.
+
+    The three tensors travel as one packed buffer ``[R, D + 2]`` so that the exchange is a single
+    collective (it is latency-bound: 266 KB per GPU for batch 8 x 64 heads x D = 128).
+    """
+    world = dist.get_world_size(group)
+    rows, d = acc.shape[:-1], acc.shape[-1]
+    packed = torch.cat([acc.reshape(-1, d), m.reshape(-1, 1), l.reshape(-1, 1)], dim=1).contiguous()
+    flat = torch.empty((world * packed.shape[0], packed.shape[1]), dtype=packed.dtype, device=packed.device)
+    dist.all_gather_into_tensor(flat, packed, group=group)
+    out = flat.view(world, packed.shape[0], packed.shape[1])
+    acc_all = out[:, :, :d].reshape((world,) + tuple(rows) + (d,))
+    m_all = out[:, :, d].reshape((world,) + tuple(rows))
+    l_all = out[:, :, d + 1].reshape((world,) + tuple(rows))
+    return m_all.contiguous(), l_all.contiguous(), acc_all.contiguous()
+
+
+def decode_context_parallel(partials_fn: Callable[[], tuple], combine_fn: Callable, group=None):
+    """Long-context decode with the context of every sequence sliced across the ranks of ``group``.
+
+    ``partials_fn()`` returns this rank's ``(m, l, acc)`` over its slice (on GPUs:
+    ``paged_attention_decode_partials``); ``combine_fn(m_all, l_all, acc_all)`` merges the gathered
+    stacks along their leading axis (on GPUs: ``lse_combine``).  Every rank ends up with the full result.
+    """
+    m, l, acc = partials_fn()
+    m_all, l_all, acc_all = all_gather_partials(m, l, acc, group=group)
+    return combine_fn(m_all, l_all, acc_all)
