@@ -1,7 +1,7 @@
 """ctypes loader for libpal_b200.so, the C-ABI library that holds every CUDA kernel.
 
 There is no fallback: if the library is missing or does not export a symbol the header
-declares, importing this module raises.  Build it with ``python -m proxy_attention_lab_b200.build``.
+declares, importing this module raises.  Build it with ``python proxy_attention_lab_b200/build.py``.
 """
 
 from __future__ import annotations
@@ -59,7 +59,7 @@ def _load() -> ctypes.CDLL:
     if not LIB_PATH.exists():
         raise ImportError(
             f"{LIB_PATH} not found: the CUDA library has not been built "
-            "(run `python -m proxy_attention_lab_b200.build`); there is no CPU fallback"
+            "(run `python proxy_attention_lab_b200/build.py`); there is no CPU fallback"
         )
     lib = ctypes.CDLL(str(LIB_PATH))
     for name, (restype, argtypes) in SIGNATURES.items():

@@ -1,6 +1,6 @@
 """Build libpal_b200.so (CUDA kernels + C ABI) in-tree with nvcc for sm_100a.
 
-Usage: ``python -m proxy_attention_lab_b200.build [--force] [--verbose]``.
+Usage: ``python proxy_attention_lab_b200/build.py [--force] [--verbose]``.
 The library is written next to this file so that it travels with the source tree.
 """
 
