@@ -106,6 +106,21 @@ int pal_paged_attention_decode(const void* queries, const void* k_pool, const vo
                                float scale, int dtype, int partition_pages, void* workspace,
                                size_t workspace_bytes, void* stream);
 
+/* Same operation with the workspace taken from a PAL_STATIC_SCRATCH_BYTES array built into the library,
+ * for hosts that own nothing but the tensors they were given (device memory fully committed to the page
+ * pools, or a plugin interface with no way to request temporaries) and so cannot supply a workspace.
+ * No counterpart in the reference, whose MLX allocator always hands its primitives scratch buffers.
+ * The call allocates nothing.  It fails with PAL_ERR_WORKSPACE when the problem needs more than
+ * PAL_STATIC_SCRATCH_BYTES (see pal_decode_workspace_bytes).  All calls on one GPU share the array and
+ * it keeps the previous call's contents: calls that overlap on a GPU race, so serialise them.  The first
+ * call on each device resolves the array's device address; make that call outside any stream capture. */
+#define PAL_STATIC_SCRATCH_BYTES (16u * 1024u * 1024u)
+int pal_paged_attention_decode_static(const void* queries, const void* k_pool, const void* v_pool,
+                                      const void* page_table, const int32_t* sequence_lengths, void* out,
+                                      int num_seqs, int num_q_heads, int num_kv_heads, int head_dim,
+                                      int tokens_per_page, int64_t num_pages, int max_pages_per_seq,
+                                      float scale, int dtype, int partition_pages, void* stream);
+
 /* First half of the two-pass decode, for callers that merge partials themselves (for example
  * across GPUs that each hold a slice of every sequence's context).  Runs the split-KV pass over
  * the pages this pool holds and merges its own partitions, but does not normalise: writes
