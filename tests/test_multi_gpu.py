@@ -47,13 +47,18 @@ def _worker(rank, world, port, ret):
         out = decode_context_parallel(
             lambda: pal.paged_attention_decode_partials(q, kp, vp, table.to(dev), local_len.to(dev), partition_pages=64),
             lambda m, l, a: pal.lse_combine(m, l, a, out_dtype=torch.bfloat16))
-        err_ctx = (out.float().cpu() - ref).abs().max().item()
+        def excess(o, r):
+            # worst violation of "within 2e-3 or within one bf16 unit in the last place"
+            diff = (o.float().cpu() - r).abs()
+            return (diff - torch.maximum(torch.tensor(2e-3), r.abs() * 2.0 ** -7)).max().item()
+
+        err_ctx = excess(out, ref)
         # --- kv-head sharding: no collective on the data path ---
         hk = kv_head_range(4, world, rank)
         g = 16 // 4
         o = pal.paged_attention_decode(q[:, hk.start * g:hk.stop * g].contiguous(), kp[:, hk.start:hk.stop].contiguous(),
                                        vp[:, hk.start:hk.stop].contiguous(), c.page_table.to(dev), c.lens.to(dev))
-        err_head = (o.float().cpu() - ref[:, hk.start * g:hk.stop * g]).abs().max().item()
+        err_head = excess(o, ref[:, hk.start * g:hk.stop * g])
         torch.cuda.synchronize()
         ret[rank] = (err_ctx, err_head)
     finally:
@@ -76,4 +81,4 @@ def test_context_and_head_sharding_two_gpus():
         assert p.exitcode == 0
     for r in range(2):
         err_ctx, err_head = ret[r]
-        assert err_ctx <= 2e-3 and err_head <= 2e-3, ret[r]
+        assert err_ctx <= 0 and err_head <= 0, ret[r]
