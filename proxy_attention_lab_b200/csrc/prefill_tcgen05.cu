@@ -30,9 +30,8 @@
 // overwrites its first 64 columns and is the A operand of the PV MMAs), O_q at 256 + 128 q.
 //
 // P has the input type (an fp16 A with a bf16 B is rejected by the hardware as an illegal
-// instruction).  For bf16 the softmax denominator is summed from the rounded weights, so that the
-// result is an exact weighted mean with weights perturbed by < 2^-8, and query tiles whose rows see
-// fewer than 256 keys get the rounding residual of P through a second set of PV MMAs.
+// instruction).  bf16 rounds P by up to 2^-8 relative; query tiles whose rows see fewer than 256 keys
+// get the rounding residual of P through a second set of PV MMAs (see split_p below).
 //
 // Softmax keeps a possibly stale running maximum and only rescales O when the true maximum has grown
 // by more than 2^8 (the result is exact either way: numerator and denominator use the same
@@ -173,6 +172,136 @@ __device__ __forceinline__ uint64_t make_desc(uint32_t saddr, uint32_t lbo_bytes
 __host__ __device__ constexpr uint32_t make_idesc(int n, int a_fmt, int b_fmt, int b_mn_major) {
   return (1u << 4) | ((uint32_t)a_fmt << 7) | ((uint32_t)b_fmt << 10) | ((uint32_t)b_mn_major << 16) |
          ((uint32_t)(n >> 3) << 17) | ((uint32_t)(kTile >> 4) << 24);
+}
+
+
+// ---- softmax building blocks ------------------------------------------------------------------
+// Key offset (relative to the tile's first key) held by column c of an S tile.  A history tile's
+// columns are permuted: 0-63 are slots 0-7 of pages 0-7, 64-127 slots 8-15 of the same pages.
+template <bool PAGED>
+__device__ __forceinline__ constexpr int col_key_offset(int c) {
+  return PAGED ? (((c & 63) >> 3) * kTPP + (c & 7) + ((c >> 6) << 3)) : c;
+}
+__device__ __forceinline__ float max3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
+
+// Row maximum of one thread's 128 raw scores; columns whose key offset exceeds rel_limit are ignored.
+// Four independent chains, the next 32 columns in flight while the current ones are reduced.
+template <bool PAGED, bool MASK>
+__device__ __forceinline__ float tile_row_max(uint32_t tS, int rel_limit) {
+  float m[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+  uint32_t cur[32], nxt[32];
+  tmem_ld32(tS, cur);
+  tmem_wait_ld();
+#pragma unroll
+  for (int c4 = 0; c4 < 4; ++c4) {
+    if (c4 < 3) tmem_ld32(tS + (c4 + 1) * 32, nxt);
+#pragma unroll
+    for (int i = 0; i < 32; i += 8) {
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        float a = __uint_as_float(cur[i + 2 * k]), b = __uint_as_float(cur[i + 2 * k + 1]);
+        if (MASK) {
+          if (col_key_offset<PAGED>(c4 * 32 + i + 2 * k) > rel_limit) a = -INFINITY;
+          if (col_key_offset<PAGED>(c4 * 32 + i + 2 * k + 1) > rel_limit) b = -INFINITY;
+        }
+        m[k] = max3(m[k], a, b);
+      }
+    }
+    if (c4 < 3) {
+      tmem_wait_ld();
+#pragma unroll
+      for (int i = 0; i < 32; ++i) cur[i] = nxt[i];
+    }
+  }
+  return fmaxf(fmaxf(m[0], m[1]), fmaxf(m[2], m[3]));
+}
+
+// One quarter of an S row: the 32 scores that become P columns [16u, 16u + 16), in P's key order.
+template <bool PAGED>
+__device__ __forceinline__ void load_quarter(uint32_t tS, int u, uint32_t (&v)[32]) {
+  if (PAGED) {
+    // pages 2u, 2u+1: slots 0-7 at S columns 16u.., slots 8-15 at S columns 64 + 16u..
+    uint32_t a16[16], b16[16];
+    tmem_ld16(tS + 16 * u, a16);
+    tmem_ld16(tS + 64 + 16 * u, b16);
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      v[i] = a16[i];
+      v[16 + i] = b16[i];
+    }
+  } else {
+    tmem_ld32(tS + 32 * u, v);
+  }
+}
+
+// P = exp2(s * scale - m_ref) for one row, written as packed 16-bit pairs over S's first 64 columns,
+// a quarter (32 keys -> 16 columns) at a time so that P never overtakes S columns still to be read,
+// with the next quarter's scores in flight.  SPLIT also writes the rounding residual P - round(P)
+// to columns 64..127 (after the scores living there have been consumed).
+template <typename T, bool PAGED, bool MASK, bool SPLIT>
+__device__ __forceinline__ void tile_exp_store(uint32_t tS, float scale_log2, float m_ref, int rel_limit, float& l_run) {
+  using PK = Mma16816<T>;
+  float2 acc0 = make_float2(0.f, 0.f), acc1 = make_float2(0.f, 0.f);
+  const float2 sc2 = make_float2(scale_log2, scale_log2), nm2 = make_float2(-m_ref, -m_ref);
+  uint32_t cur[32], nxt[32];
+  uint32_t lo_hold0[16], lo_hold1[16];
+  load_quarter<PAGED>(tS, 0, cur);
+  tmem_wait_ld();
+#pragma unroll
+  for (int u = 0; u < 4; ++u) {
+    if (u < 3) load_quarter<PAGED>(tS, u + 1, nxt);
+    uint32_t hi[16], lo[16];
+#pragma unroll
+    for (int w = 0; w < 16; ++w) {
+      // indices (into cur) of the two keys that land in P column 16u + w
+      const int pg = w >> 3, ww = w & 7;
+      const int i0 = PAGED ? (ww < 4 ? 8 * pg + 2 * ww : 16 + 8 * pg + 2 * (ww - 4)) : 2 * w;
+      float2 x = __ffma2_rn(make_float2(__uint_as_float(cur[i0]), __uint_as_float(cur[i0 + 1])), sc2, nm2);
+      if (MASK) {
+        const int c0 = PAGED ? (i0 < 16 ? 16 * u + i0 : 64 + 16 * u + (i0 - 16)) : 32 * u + i0;
+        if (col_key_offset<PAGED>(c0) > rel_limit) x.x = -INFINITY;
+        if (col_key_offset<PAGED>(c0 + 1) > rel_limit) x.y = -INFINITY;
+      }
+      const float2 e = make_float2(fast_exp2(x.x), fast_exp2(x.y));
+      hi[w] = PK::pack(e.x, e.y);
+      if (SPLIT) lo[w] = PK::pack_residual(e.x, e.y, hi[w]);
+      if (w & 1)
+        acc1 = __fadd2_rn(acc1, e);
+      else
+        acc0 = __fadd2_rn(acc0, e);
+    }
+    tmem_st16(tS + 16 * u, hi);
+    if (SPLIT) {
+      if (PAGED) {
+        tmem_st16(tS + 64 + 16 * u, lo);  // S columns 64 + 16u.. were consumed in this very quarter
+      } else if (u == 0) {
+#pragma unroll
+        for (int w = 0; w < 16; ++w) lo_hold0[w] = lo[w];
+      } else if (u == 1) {
+#pragma unroll
+        for (int w = 0; w < 16; ++w) lo_hold1[w] = lo[w];
+      } else if (u == 2) {
+        // S columns 64..95 are in `cur`, 96..127 are being fetched: 64..95 may be overwritten now
+        tmem_st16(tS + 64, lo_hold0);
+        tmem_st16(tS + 80, lo_hold1);
+#pragma unroll
+        for (int w = 0; w < 16; ++w) lo_hold0[w] = lo[w];
+      } else {
+        tmem_st16(tS + 96, lo_hold0);
+        tmem_st16(tS + 112, lo);
+      }
+    }
+    if (u < 3) {
+      tmem_wait_ld();
+#pragma unroll
+      for (int i = 0; i < 32; ++i) cur[i] = nxt[i];
+    }
+  }
+  l_run += (acc0.x + acc0.y) + (acc1.x + acc1.y);
 }
 
 template <typename T>
@@ -435,7 +564,6 @@ __global__ void __launch_bounds__(64 + 128 * NQ, 1)
     const int qi = t0 + row;                    // index of this row's query token in its sequence
     float m_used = -INFINITY, l_run = 0.f;
     bool ok = true;
-    using PK = Mma16816<T>;  // P is stored in the input type
 
     for (int j = 0; j < num_tiles; ++j) {
       const bool paged = j < hist_tiles;
@@ -443,37 +571,16 @@ __global__ void __launch_bounds__(64 + 128 * NQ, 1)
       if (!(ok = mbar_wait(&s_full[q], j & 1, p.status))) break;
       tc_fence_after();
       if (tid == 64) PAL_MARK(p, 8, 1u + j);
-      // which columns need masking at all (warp-uniform)
+      // which columns need masking at all (warp-uniform), and up to which key offset this row sees
       const bool need_mask = paged ? ((j + 1) * kTile > H) : (jd == dense_tiles - 1 || (jd + 1) * kTile > N);
-
-      // visibility of column `c` (0..127) of the S tile for this row
-      auto visible = [&](int c) -> bool {
-        if (paged) {
-          // columns 0-63: slots 0-7 of pages 0-7; columns 64-127: slots 8-15 of pages 0-7
-          const int tok = j * kTile + ((c & 63) >> 3) * kTPP + (c & 7) + ((c >> 6) << 3);
-          return tok < H;
-        }
-        const int key = jd * kTile + c;
-        return key <= qi && key < N;
-      };
+      const int rel_limit = paged ? (H - 1 - j * kTile) : (min(qi, N - 1) - jd * kTile);
 
       // ---- pass 1: row maximum of the scaled scores ----
-      float mx = -INFINITY;
-#pragma unroll
-      for (int c4 = 0; c4 < 4; ++c4) {
-        uint32_t v[32];
-        tmem_ld32(tS + c4 * 32, v);
-        tmem_wait_ld();
-        if (need_mask) {
-#pragma unroll
-          for (int i = 0; i < 32; ++i)
-            if (visible(c4 * 32 + i)) mx = fmaxf(mx, __uint_as_float(v[i]));
-        } else {
-#pragma unroll
-          for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(v[i]));
-        }
-      }
-      if (tid == 64) PAL_MARK(p, 9, 1u + j);
+      float mx;
+      if (paged)
+        mx = need_mask ? tile_row_max<true, true>(tS, rel_limit) : tile_row_max<true, false>(tS, rel_limit);
+      else
+        mx = need_mask ? tile_row_max<false, true>(tS, rel_limit) : tile_row_max<false, false>(tS, rel_limit);
       mx *= p.scale_log2;  // scale > 0, so the maximum commutes with the scaling
       const float m_new = fmaxf(m_used, mx);
       if (j == 0) {
@@ -498,74 +605,22 @@ __global__ void __launch_bounds__(64 + 128 * NQ, 1)
       }
       const float m_ref = m_used > -INFINITY ? m_used : 0.f;
 
-      // ---- pass 2: P = exp2(s * scale - m) in the input type, packed two per column over S's first
-      // 64 columns, a quarter (32 keys -> 16 columns) at a time so that P never overtakes the S columns
-      // still to be read.  With split_p the rounding residual P - round(P) goes to columns 64..127.
-      uint32_t lo_hold[2][16];
-#pragma unroll
-      for (int u = 0; u < 4; ++u) {
-        uint32_t v[32];
-        if (paged) {
-          // pages 2u, 2u+1: slots 0-7 at columns 16u.., slots 8-15 at columns 64+16u..
-          uint32_t a16[16], b16[16];
-          tmem_ld16(tS + 16 * u, a16);
-          tmem_ld16(tS + 64 + 16 * u, b16);
-          tmem_wait_ld();
-#pragma unroll
-          for (int i = 0; i < 16; ++i) {
-            v[i] = a16[i];
-            v[16 + i] = b16[i];
-          }
-        } else {
-          tmem_ld32(tS + 32 * u, v);
-          tmem_wait_ld();
-        }
-        float e[32];
-#pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          float x = fast_exp2(fmaf(__uint_as_float(v[i]), p.scale_log2, -m_ref));
-          if (need_mask) {
-            const int c = paged ? (i < 16 ? 16 * u + i : 64 + 16 * u + (i - 16)) : 32 * u + i;
-            if (!visible(c)) x = 0.f;
-          }
-          e[i] = x;
-        }
-        uint32_t hi[16], lo[16];
-#pragma unroll
-        for (int w = 0; w < 16; ++w) {
-          // element pair that lands in P column 16u + w (indices are compile-time, values selected)
-          const int pg = w >> 3, ww = w & 7;  // paged: page 2u + pg, column ww of its 8
-          const int ip = ww < 4 ? 8 * pg + 2 * ww : 16 + 8 * pg + 2 * (ww - 4);
-          const float x0 = paged ? e[ip] : e[2 * w];
-          const float x1 = paged ? e[ip + 1] : e[2 * w + 1];
-          hi[w] = PK::pack(x0, x1);
-          if (split_p) {
-            lo[w] = PK::pack_residual(x0, x1, hi[w]);
-            l_run += x0 + x1;
-          } else if (PK::kSplitP) {
-            // normalise with the weights the MMA will really use: bf16(p), not p
-            l_run += __uint_as_float(hi[w] << 16) + __uint_as_float(hi[w] & 0xffff0000u);
-          } else {
-            l_run += x0 + x1;
-          }
-        }
-        tmem_st16(tS + 16 * u, hi);
-        if (split_p) {
-          if (paged) {
-            tmem_st16(tS + 64 + 16 * u, lo);  // columns 64+16u.. were consumed in this very quarter
-          } else if (u < 2) {
-#pragma unroll
-            for (int w = 0; w < 16; ++w) lo_hold[u][w] = lo[w];
-          } else if (u == 2) {
-            tmem_st16(tS + 64, lo_hold[0]);
-            tmem_st16(tS + 80, lo_hold[1]);
-#pragma unroll
-            for (int w = 0; w < 16; ++w) lo_hold[0][w] = lo[w];
-          } else {
-            tmem_st16(tS + 96, lo_hold[0]);
-            tmem_st16(tS + 112, lo);
-          }
-        }
+      // ---- pass 2: P = exp2(s * scale - m), packed over S's first 64 columns ----
+      if (split_p) {
+        if (paged)
+          tile_exp_store<T, true, true, Mma16816<T>::kSplitP>(tS, p.scale_log2, m_ref, rel_limit, l_run);
+        else
+          tile_exp_store<T, false, true, Mma16816<T>::kSplitP>(tS, p.scale_log2, m_ref, rel_limit, l_run);
+      } else if (paged) {
+        if (need_mask)
+          tile_exp_store<T, true, true, false>(tS, p.scale_log2, m_ref, rel_limit, l_run);
+        else
+          tile_exp_store<T, true, false, false>(tS, p.scale_log2, m_ref, rel_limit, l_run);
+      } else {
+        if (need_mask)
+          tile_exp_store<T, false, true, false>(tS, p.scale_log2, m_ref, rel_limit, l_run);
+        else
+          tile_exp_store<T, false, false, false>(tS, p.scale_log2, m_ref, rel_limit, l_run);
       }
       tmem_wait_st();
       if (tid == 64) PAL_MARK(p, 10, 1u + j);
