@@ -7,10 +7,12 @@ declares, importing this module raises.  Build it with ``python proxy_attention_
 from __future__ import annotations
 
 import ctypes
+import os
 from ctypes import c_char_p, c_float, c_int, c_int64, c_size_t, c_void_p
 from pathlib import Path
 
-LIB_PATH = Path(__file__).resolve().parent / "libpal_b200.so"
+# PAL_B200_LIB selects another build of the library (for A/B comparisons of kernel variants)
+LIB_PATH = Path(os.environ.get("PAL_B200_LIB") or (Path(__file__).resolve().parent / "libpal_b200.so"))
 
 PAL_OK = 0
 PAL_ERR_BAD_ARG = -1
