@@ -222,7 +222,21 @@ __global__ void __launch_bounds__(kDecodeThreads, 2) paged_decode_kernel(const D
         ok = __shfl_sync(0xffffffffu, ok, 0);
         if (!ok) return;
       }
-      it += npg;
+      // Pad the item to a multiple of four pages with empty hand-shakes, so that local page j always
+      // goes to warp j % 4 whatever the CTA processed before: the summation order of a work item, and
+      // with it every output bit, is then independent of how items were scheduled.
+      const int npg_pad = (npg + kConsumerWarps - 1) & ~(kConsumerWarps - 1);
+      if (lane == 0) {
+        for (int j = npg; j < npg_pad && ok; ++j) {
+          const uint32_t n = it + j;
+          const uint32_t stage = n % NST;
+          ok = mbar_wait(&empty_bar[stage], ((n / NST) & 1) ^ 1, status);
+          if (ok) mbar_arrive(&full_bar[stage]);
+        }
+      }
+      ok = __shfl_sync(0xffffffffu, ok, 0);
+      if (!ok) return;
+      it += npg_pad;
     }
     return;
   }
@@ -267,11 +281,18 @@ __global__ void __launch_bounds__(kDecodeThreads, 2) paged_decode_kernel(const D
 #pragma unroll
     for (int i = 0; i < MTILES; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
 
-    // page n (counted over the whole kernel) belongs to warp n % 4 and lives in stage n % NST
-    for (int j = (warp - (int)(it & 3)) & 3; j < npg; j += kConsumerWarps) {
+    // Page n (counted over the whole kernel, items padded to multiples of four) lives in stage n % NST
+    // and belongs to warp n % 4; `it` is a multiple of four, so local page j goes to warp j % 4.
+    const int npg_pad = (npg + kConsumerWarps - 1) & ~(kConsumerWarps - 1);
+    for (int j = warp; j < npg_pad; j += kConsumerWarps) {
       const uint32_t n = it + j;
       const uint32_t stage = n % NST;
       if (!mbar_wait(&full_bar[stage], (n / NST) & 1, status)) return;
+      if (j >= npg) {  // padding hand-shake: nothing was copied
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&empty_bar[stage]);
+        continue;
+      }
       const uint32_t kb = smem_u32(stages + stage * SM::kStageBytes);
       const uint32_t vb = kb + SM::kBlockBytes;
       const int tok0 = (pb + j) * TPP;
@@ -363,7 +384,7 @@ __global__ void __launch_bounds__(kDecodeThreads, 2) paged_decode_kernel(const D
       __syncwarp();
       if (lane == 0) mbar_arrive(&empty_bar[stage]);
     }
-    it += npg;
+    it += npg_pad;
 
     // ---- merge the four warps' partial states ----
 #pragma unroll
