@@ -35,6 +35,8 @@ WORKLOADS = {
                        desc="Llama-3-70B long decode: batch 8, context 131072, 64q/8kv heads, D=128, bf16, TPP=16, two-pass 256-page partitions"),
     "prefill_8b": dict(kind="prefill", S=8, n=2048, hlo=0, hhi=4096, hq=32, hkv=8, d=128, tpp=16,
                        desc="Llama-3-8B chunked causal prefill: 8 x 2048 new tokens, history U[0,4096], 32q/8kv heads, D=128, bf16, TPP=16"),
+    "prefill_small": dict(kind="prefill", S=2, n=1024, hlo=0, hhi=2048, hq=32, hkv=8, d=128, tpp=16,
+                          desc="reduced chunked prefill for profiler captures: 2 x 1024 new tokens, history U[0,2048], 32q/8kv heads, D=128, bf16, TPP=16"),
     "fill": dict(kind="fill", S=64, n=512, hkv=8, d=128, tpp=16, pages=65536,
                  desc="fill_kv_pages: 64 x 512 tokens, 8 kv heads, D=128, bf16, TPP=16, 65536-page pool, random free slots"),
 }
