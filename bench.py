@@ -33,6 +33,9 @@ WORKLOADS = {
                       desc="Llama-3-8B decode: batch 64, context U[1024,8192], 32q/8kv heads, D=128, bf16, TPP=16, fused single pass"),
     "decode_70b": dict(kind="decode", S=8, lo=131072, hi=131072, hq=64, hkv=8, d=128, tpp=16, partition_pages=256,
                        desc="Llama-3-70B long decode: batch 8, context 131072, 64q/8kv heads, D=128, bf16, TPP=16, two-pass 256-page partitions"),
+    "decode_70b_ctx": dict(kind="decode", S=8, lo=131072, hi=131072, hq=64, hkv=8, d=128, tpp=16, partition_pages=256, ctx_sharded=True,
+                           desc="Llama-3-70B long decode, context sharded: batch 8, context 131072 cut into N contiguous slices (one per GPU), "
+                                "64q/8kv heads, D=128, bf16, TPP=16, 256-page partitions, per-GPU (m,l,acc) all-gathered over NCCL and merged"),
     "prefill_8b": dict(kind="prefill", S=8, n=2048, hlo=0, hhi=4096, hq=32, hkv=8, d=128, tpp=16,
                        desc="Llama-3-8B chunked causal prefill: 8 x 2048 new tokens, history U[0,4096], 32q/8kv heads, D=128, bf16, TPP=16"),
     "prefill_small": dict(kind="prefill", S=2, n=1024, hlo=0, hhi=2048, hq=32, hkv=8, d=128, tpp=16,
@@ -356,6 +359,11 @@ def main():
     extra_cfg = {}
     if kind == "decode":
         hkv_local = None
+        ctx = bool(cfg.get("ctx_sharded"))
+        if ctx:
+            scaling = "strong"
+            extra_cfg["parallelism"] = f"context sharded x{world}: partials + one NCCL all-gather + LSE combine per step"
+            cfg = dict(cfg, lo=cfg["lo"] // world, hi=cfg["hi"] // world)  # this rank's slice of every sequence
         if args.workload == "decode_70b" and world > 1:
             # total work fixed: each GPU owns Hkv/N kv heads (and their query heads) of every sequence
             hkv_local, scaling = cfg["hkv"] // world, "strong"
@@ -364,9 +372,24 @@ def main():
             extra_cfg["parallelism"] = f"sequence sharded x{world} (each GPU its own batch of {cfg['S']}), no collective"
         data = build_decode(cfg, device, seed=rank if hkv_local is None else 0, hkv_local=hkv_local)
         pp = cfg["partition_pages"]
+        if ctx:
+            from proxy_attention_lab_b200.sharding import all_gather_partials
+
+            if world > 1:  # every rank must hold the same queries
+                dist.broadcast(data["q"], src=0)
+
+        def decode_call(q, table, lens):
+            if not ctx:
+                return pal.paged_attention_decode(q, data["k_pool"], data["v_pool"], table, lens, partition_pages=pp)
+            m, l, acc = pal.paged_attention_decode_partials(q, data["k_pool"], data["v_pool"], table, lens, partition_pages=pp)
+            if world > 1:
+                m, l, acc = all_gather_partials(m, l, acc)
+            else:
+                m, l, acc = m[None], l[None], acc[None]
+            return pal.lse_combine(m, l, acc, out_dtype=torch.bfloat16)
 
         def step():
-            return pal.paged_attention_decode(data["q"], data["k_pool"], data["v_pool"], data["table"], data["lens"], partition_pages=pp)
+            return decode_call(data["q"], data["table"], data["lens"])
 
         q_dev, t_dev, l_dev = torch.empty_like(data["q"]), torch.empty_like(data["table"]), torch.empty_like(data["lens"])
         out_host = torch.empty((cfg["S"], data["hq"], cfg["d"]), dtype=torch.bfloat16).pin_memory()
@@ -375,14 +398,14 @@ def main():
             q_dev.copy_(data["q_host"], non_blocking=True)
             t_dev.copy_(data["table_host"], non_blocking=True)
             l_dev.copy_(data["lens_host"], non_blocking=True)
-            out = pal.paged_attention_decode(q_dev, data["k_pool"], data["v_pool"], t_dev, l_dev, partition_pages=pp)
+            out = decode_call(q_dev, t_dev, l_dev)
             out_host.copy_(out, non_blocking=True)
 
         h2d = data["q_host"].numel() * 2 + data["table_host"].numel() * 4 + data["lens_host"].numel() * 4
         d2h = out_host.numel() * 2
         units_per_step, alg_per_step = data["kv_bytes"], data["alg_bytes"]
         to_value = lambda units, sec: units / sec / 1e9
-        launches_per_step = 2 if pp else 1
+        launches_per_step = (3 if ctx else 2) if pp else 1
         bound, peak = "hbm", peaks["hbm"]
         achieved_of = lambda sec: alg_per_step / sec / 1e9
         roof_unit = "GB/s"
@@ -390,8 +413,11 @@ def main():
     elif kind == "prefill":
         seqs = None
         if world > 1:
-            per = max(cfg["S"] // world, 1)
-            seqs = list(range(rank * per, min((rank + 1) * per, cfg["S"]))) or [rank % cfg["S"]]
+            from proxy_attention_lab_b200.sharding import partition_sequences
+
+            hist_all = make_lengths(0, cfg["S"], cfg["hlo"], cfg["hhi"])
+            work = [cfg["n"] * int(h) + cfg["n"] * (cfg["n"] + 1) // 2 for h in hist_all]
+            seqs = partition_sequences(work, world)[rank] or [rank % cfg["S"]]
             scaling = "strong"
             extra_cfg["parallelism"] = f"sequence sharded x{world}, no collective"
         data = build_prefill(cfg, device, seed=0, seqs=seqs)
@@ -473,7 +499,7 @@ def main():
 
     total_units, total_tokens = units_per_step, data["tokens"]
     if world > 1:
-        kv_head_sharded = args.workload == "decode_70b"
+        kv_head_sharded = args.workload in ("decode_70b", "decode_70b_ctx")
         t = torch.tensor([float(units_per_step), 0.0 if kv_head_sharded else float(data["tokens"])], device=device, dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.SUM)
         total_units = float(t[0].item())
