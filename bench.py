@@ -368,7 +368,7 @@ def main():
             # total work fixed: each GPU owns Hkv/N kv heads (and their query heads) of every sequence
             hkv_local, scaling = cfg["hkv"] // world, "strong"
             extra_cfg["parallelism"] = f"kv-head sharded x{world}, no collective"
-        elif world > 1:
+        elif world > 1 and not ctx:
             extra_cfg["parallelism"] = f"sequence sharded x{world} (each GPU its own batch of {cfg['S']}), no collective"
         data = build_decode(cfg, device, seed=rank if hkv_local is None else 0, hkv_local=hkv_local)
         pp = cfg["partition_pages"]
