@@ -42,6 +42,9 @@ WORKLOADS = {
                           desc="reduced chunked prefill for profiler captures: 2 x 1024 new tokens, history U[0,2048], 32q/8kv heads, D=128, bf16, TPP=16"),
     "fill": dict(kind="fill", S=64, n=512, hkv=8, d=128, tpp=16, pages=65536,
                  desc="fill_kv_pages: 64 x 512 tokens, 8 kv heads, D=128, bf16, TPP=16, 65536-page pool, random free slots"),
+    "fill_append": dict(kind="fill", S=64, n=512, hkv=8, d=128, tpp=16, pages=65536, append=True, hhi=4096,
+                        desc="fill_kv_pages: prefill append, 64 sequences x 512 consecutive positions after a history U[0,4096], random pages, "
+                             "8 kv heads, D=128, bf16, TPP=16, 65536-page pool"),
 }
 
 
@@ -191,7 +194,15 @@ def build_fill(cfg, device, seed):
     keys = torch.randn((T, hkv, d), device=device, dtype=torch.bfloat16, generator=gen)
     vals = torch.randn((T, hkv, d), device=device, dtype=torch.bfloat16, generator=gen)
     g = torch.Generator().manual_seed(seed + 1)
-    slots = torch.randperm(P * tpp, generator=g)[:T]
+    if cfg.get("append"):
+        # every sequence appends n consecutive positions after its history; its blocks sit on random distinct pages
+        hist = torch.randint(0, cfg["hhi"], (cfg["S"],), generator=g)
+        pos = hist[:, None] + torch.arange(cfg["n"])[None, :]
+        blocks_per_seq = (cfg["hhi"] + cfg["n"]) // tpp + 1
+        pages = torch.randperm(P, generator=g)[: cfg["S"] * blocks_per_seq].reshape(cfg["S"], blocks_per_seq)
+        slots = (torch.gather(pages, 1, pos // tpp) * tpp + pos % tpp).reshape(-1)
+    else:
+        slots = torch.randperm(P * tpp, generator=g)[:T]
     k_pool = torch.zeros((P, hkv, d // 8, tpp, 8), device=device, dtype=torch.bfloat16)
     v_pool = torch.zeros((P, hkv, d, tpp), device=device, dtype=torch.bfloat16)
     return dict(keys=keys, vals=vals, slots=slots.to(device), k_pool=k_pool, v_pool=v_pool, alg_bytes=4 * T * hkv * d * 2 + 8 * T, tokens=T,

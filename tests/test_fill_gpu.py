@@ -99,6 +99,35 @@ def test_scatter_config_reference_triple(pal, cuda):
     assert _bit_equal(gk.cpu(), ek) and _bit_equal(gv.cpu(), ev)
 
 
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("hkv,d,tpp", [(8, 128, 16), (2, 64, 32), (1, 32, 8), (3, 80, 16), (8, 256, 16), (4, 128, 4), (32, 256, 16)])
+def test_runs_mixed_with_scattered_and_skipped_tokens(pal, cuda, dtype, hkv, d, tpp):
+    """Token lists that mix appended runs (aligned and not), isolated tokens and slots that must be skipped, with a
+    length that is not a multiple of the kernel's token group: both store paths and their edges, bit for bit."""
+    P = 96
+    g = torch.Generator().manual_seed(hkv * 1000 + d + tpp)
+    pages = torch.randperm(P, generator=g).tolist()
+    slots = []
+    for start, n in ((0, 40), (5, 23), (tpp - 1, 3), (3, 1), (8 % tpp, 8), (0, tpp), (1, 2 * tpp + 7)):
+        pgs = [pages.pop() for _ in range((start + n) // tpp + 1)]
+        slots += [pgs[(start + i) // tpp] * tpp + (start + i) % tpp for i in range(n)]
+        slots += [-1, P * tpp + 3]  # skipped entries between the runs
+        slots += [pages.pop() * tpp + int(torch.randint(0, tpp, (1,), generator=g))]  # an isolated token
+    slots = torch.tensor(slots, dtype=torch.int64)
+    T = slots.numel()
+    assert T % 16 != 0
+    keys = torch.randn((T, hkv, d), generator=g).to(dtype)
+    vals = torch.randn((T, hkv, d), generator=g).to(dtype)
+    k, v = _pools(P, hkv, d, tpp, dtype, sentinel=0x3C3C)
+    valid = (slots >= 0) & (slots < P * tpp)  # the library skips the others; the oracle is given only the valid ones
+    ek, ev = fill_kv_pages_oracle(keys[valid], vals[valid], k, v, slots[valid])
+    gk, gv = pal.fill_kv_pages(keys.to(cuda), vals.to(cuda), k.to(cuda), v.to(cuda), slots.to(cuda))
+    assert _bit_equal(gk.cpu(), ek) and _bit_equal(gv.cpu(), ev)
+    # a reversed list has the same destinations but no ascending runs
+    rk, rv = pal.fill_kv_pages(keys.flip(0).to(cuda), vals.flip(0).to(cuda), k.to(cuda), v.to(cuda), slots.flip(0).to(cuda))
+    assert _bit_equal(rk.cpu(), ek) and _bit_equal(rv.cpu(), ev)
+
+
 def test_empty_and_functional_forms(pal, cuda):
     dtype = torch.float16
     k, v = _pools(2, 2, 32, 4, dtype, sentinel=0x0F0F)
