@@ -12,7 +12,9 @@
 //   warp 0        producer: Q / dense K / dense V tiles by TMA (128-byte swizzle); history K pages
 //                 by cp.async.bulk (4 KiB each, the pool's native striped block) and history V pages
 //                 by TMA with the 32-byte swizzle; two-stage K ring and two-stage V ring.
-//   warp 1        one thread issues every tcgen05.mma and tcgen05.commit.
+//   warp 1        issues every tcgen05.mma and tcgen05.commit: the warp stays converged and the thread picked by
+//                 elect.sync issues, which lets the compiler keep descriptors in uniform registers (a branch
+//                 on lane 0 instead costs several hundred cycles of the issuing thread per key tile).
 //   warps 2..     one softmax warpgroup (128 threads = 128 rows = 128 TMEM lanes) per query head.
 //
 // Shared-memory operand layouts and their UMMA descriptors
@@ -98,6 +100,11 @@ __device__ __forceinline__ void tma_load_3d(void* dst, const CUtensorMap* map, i
           smem_u32(dst)),
       "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2)
       : "memory");
+}
+__device__ __forceinline__ bool elect_one() {
+  uint32_t pred;
+  asm volatile("{\n\t.reg .pred p;\n\telect.sync _|p, 0xffffffff;\n\tselp.b32 %0, 1, 0, p;\n\t}" : "=r"(pred));
+  return pred != 0;
 }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
@@ -460,38 +467,49 @@ __global__ void __launch_bounds__(64 + 128 * NQ, 1)
     }
   } else if (warp == 1) {
     // =============================== MMA issuer ===============================
-    if (lane == 0) {
+    {
       constexpr int F = Fmt<T>::kCode;
       constexpr uint32_t idesc_qk128 = make_idesc(128, F, F, 0);
       constexpr uint32_t idesc_qk64 = make_idesc(64, F, F, 0);
       constexpr uint32_t idesc_pv_paged = make_idesc(128, F, F, 0);  // A = P (TMEM), B = V K-major
       constexpr uint32_t idesc_pv_dense = make_idesc(128, F, F, 1);  // B = V MN-major
       const uint32_t sQ_u = smem_u32(sQ), sK_u = smem_u32(sK), sV_u = smem_u32(sV);
+      // Descriptors of the operand tiles, built once; an MMA's descriptor is one of these plus a constant
+      // (the start-address field counts 16-byte units and sits in the low bits, so a byte offset adds >> 4).
+      uint64_t q_desc[NQ], k_dense[2], k_hist[2], v_dense[2], v_hist[2];
+#pragma unroll
+      for (int q = 0; q < NQ; ++q) q_desc[q] = make_desc(sQ_u + q * kTileBytes, 16, 1024, kLayoutSw128);
+#pragma unroll
+      for (int st = 0; st < 2; ++st) {
+        k_dense[st] = make_desc(sK_u + st * kTileBytes, 16, 1024, kLayoutSw128);
+        k_hist[st] = make_desc(sK_u + st * kTileBytes, 256, kPageBytes, kLayoutNone);
+        v_dense[st] = make_desc(sV_u + st * kTileBytes, kHalfTileBytes, 1024, kLayoutSw128);
+        v_hist[st] = make_desc(sV_u + st * kTileBytes, 16, 256, kLayoutSw32);
+      }
       bool ok = mbar_wait(q_full, 0, p.status);
       PAL_MARK(p, 4, 1u + ok);
 
       // S_q(j) = Q_q . K(j)^T into TMEM columns [128 q, 128 q + 128)
       auto issue_qk = [&](int q, int j) {
+        if (!elect_one()) return;
         const int st = j & 1;
         const uint32_t d_tmem = tmem_base + q * kTile;
-        const uint32_t qa = sQ_u + q * kTileBytes;
-        const uint32_t kbase = sK_u + st * kTileBytes;
+        const uint64_t qa = q == 0 ? q_desc[0] : q_desc[NQ - 1];
         if (j < hist_tiles) {
+          const uint64_t kb = st ? k_hist[1] : k_hist[0];
 #pragma unroll
           for (int ks = 0; ks < kD / 16; ++ks) {
-            const uint64_t a = make_desc(qa + (ks >> 2) * kHalfTileBytes + (ks & 3) * 32, 16, 1024, kLayoutSw128);
+            const uint64_t a = qa + (uint64_t)(((ks >> 2) * kHalfTileBytes + (ks & 3) * 32) >> 4);
 #pragma unroll
-            for (int half = 0; half < 2; ++half) {
-              const uint64_t b = make_desc(kbase + half * 128 + ks * 512, 256, kPageBytes, kLayoutNone);
-              tc_mma_ss(d_tmem + half * 64, a, b, idesc_qk64, ks > 0);
-            }
+            for (int half = 0; half < 2; ++half)
+              tc_mma_ss(d_tmem + half * 64, a, kb + (uint64_t)((half * 128 + ks * 512) >> 4), idesc_qk64, ks > 0);
           }
         } else {
+          const uint64_t kb = st ? k_dense[1] : k_dense[0];
 #pragma unroll
           for (int ks = 0; ks < kD / 16; ++ks) {
-            const uint64_t a = make_desc(qa + (ks >> 2) * kHalfTileBytes + (ks & 3) * 32, 16, 1024, kLayoutSw128);
-            const uint64_t b = make_desc(kbase + (ks >> 2) * kHalfTileBytes + (ks & 3) * 32, 16, 1024, kLayoutSw128);
-            tc_mma_ss(d_tmem, a, b, idesc_qk128, ks > 0);
+            const uint64_t off = (uint64_t)(((ks >> 2) * kHalfTileBytes + (ks & 3) * 32) >> 4);
+            tc_mma_ss(d_tmem, qa + off, kb + off, idesc_qk128, ks > 0);
           }
         }
         PAL_MARK(p, 6, 1u + j);
@@ -500,24 +518,22 @@ __global__ void __launch_bounds__(64 + 128 * NQ, 1)
       };
       // O_q += P_q(j) . V(j)
       auto issue_pv = [&](int q, int j) {
+        if (!elect_one()) return;
         const int st = j & 1;
         const uint32_t d_tmem = tmem_base + 2 * kTile + q * kTile;
         const uint32_t a_tmem = tmem_base + q * kTile;  // P over the first 64 columns of S_q
-        const uint32_t vbase = sV_u + st * kTileBytes;
         for (int part = 0; part < (split_p ? 2 : 1); ++part) {  // part 1: the residual of P, 64 columns on
           const uint32_t a_part = a_tmem + part * 64;
           if (j < hist_tiles) {
+            const uint64_t vb = st ? v_hist[1] : v_hist[0];
 #pragma unroll
-            for (int pg = 0; pg < kPagesPerTile; ++pg) {
-              const uint64_t b = make_desc(vbase + pg * kPageBytes, 16, 256, kLayoutSw32);
-              tc_mma_ts(d_tmem, a_part + pg * 8, b, idesc_pv_paged, (j > 0 || pg > 0 || part > 0));
-            }
+            for (int pg = 0; pg < kPagesPerTile; ++pg)
+              tc_mma_ts(d_tmem, a_part + pg * 8, vb + (uint64_t)((pg * kPageBytes) >> 4), idesc_pv_paged, (j > 0 || pg > 0 || part > 0));
           } else {
+            const uint64_t vb = st ? v_dense[1] : v_dense[0];
 #pragma unroll
-            for (int kk = 0; kk < kTile / 16; ++kk) {
-              const uint64_t b = make_desc(vbase + kk * 2048, kHalfTileBytes, 1024, kLayoutSw128);
-              tc_mma_ts(d_tmem, a_part + kk * 8, b, idesc_pv_dense, (j > 0 || kk > 0 || part > 0));
-            }
+            for (int kk = 0; kk < kTile / 16; ++kk)
+              tc_mma_ts(d_tmem, a_part + kk * 8, vb + (uint64_t)((kk * 2048) >> 4), idesc_pv_dense, (j > 0 || kk > 0 || part > 0));
           }
         }
         PAL_MARK(p, 12, 1u + j);
@@ -530,7 +546,7 @@ __global__ void __launch_bounds__(64 + 128 * NQ, 1)
       if (ok) {
         tc_fence_after();
         for (int q = 0; q < NQ; ++q) issue_qk(q, 0);
-        tc_commit(&k_empty[0]);
+        if (elect_one()) tc_commit(&k_empty[0]);
       }
       for (int j = 0; j < num_tiles && ok; ++j) {
         const int st = j & 1;
@@ -547,10 +563,11 @@ __global__ void __launch_bounds__(64 + 128 * NQ, 1)
               tc_fence_after();
             }
             issue_qk(q, j + 1);
-            if (q == NQ - 1) tc_commit(&k_empty[(j + 1) & 1]);
+            if (q == NQ - 1 && elect_one()) tc_commit(&k_empty[(j + 1) & 1]);
           }
         }
-        if (ok) tc_commit(&v_empty[st]);
+        __syncwarp();
+        if (ok && elect_one()) tc_commit(&v_empty[st]);
       }
     }
   } else {
