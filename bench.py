@@ -42,6 +42,9 @@ WORKLOADS = {
                           desc="reduced chunked prefill for profiler captures: 2 x 1024 new tokens, history U[0,2048], 32q/8kv heads, D=128, bf16, TPP=16"),
     "fill": dict(kind="fill", S=64, n=512, hkv=8, d=128, tpp=16, pages=65536,
                  desc="fill_kv_pages: 64 x 512 tokens, 8 kv heads, D=128, bf16, TPP=16, 65536-page pool, random free slots"),
+    "fill_append_small": dict(kind="fill", S=48, n=1024, hkv=8, d=128, tpp=16, pages=16384, append=True, hhi=4096,
+                              desc="reduced prefill append for profiler captures: 48 sequences x 1024 consecutive positions after a history U[0,4096], "
+                                   "8 kv heads, D=128, bf16, TPP=16, 16384-page pool"),
     "fill_append": dict(kind="fill", S=64, n=512, hkv=8, d=128, tpp=16, pages=65536, append=True, hhi=4096,
                         desc="fill_kv_pages: prefill append, 64 sequences x 512 consecutive positions after a history U[0,4096], random pages, "
                              "8 kv heads, D=128, bf16, TPP=16, 65536-page pool"),

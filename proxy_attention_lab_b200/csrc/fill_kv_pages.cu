@@ -76,6 +76,11 @@ __global__ void __launch_bounds__(256) fill_kv_pages_kernel(
 
 constexpr int kGroupTokens = 16;
 
+__device__ __forceinline__ void cp_async_16(void* smem_dst, const void* gmem_src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(smem_dst)), "l"(gmem_src)
+               : "memory");
+}
+
 // (page, slot) of token t, or page = -1 when the token has to be skipped
 template <bool kSlots>
 __device__ __forceinline__ void token_destination(long long t, const int64_t* slot_mapping, const uint32_t* page_table,
@@ -107,7 +112,8 @@ __global__ void __launch_bounds__(256) fill_kv_pages_grouped_kernel(
     const uint4* __restrict__ new_keys, const uint4* __restrict__ new_values, uint16_t* __restrict__ k_pool,
     uint16_t* __restrict__ v_pool, const int64_t* __restrict__ slot_mapping, const uint32_t* __restrict__ page_table,
     const int32_t* __restrict__ write_positions, const uint32_t* __restrict__ query_to_seq_map, long long num_tokens,
-    int num_seqs, int num_kv_heads, int head_dim, int tokens_per_page, long long num_pages, int max_pages_per_seq) {
+    int num_seqs, int num_kv_heads, int head_dim, int tokens_per_page, long long num_pages, int max_pages_per_seq,
+    int parts) {
   extern __shared__ __align__(16) unsigned char fill_smem[];
   __shared__ long long s_page[kGroupTokens];
   __shared__ int s_slot[kGroupTokens];
@@ -116,12 +122,16 @@ __global__ void __launch_bounds__(256) fill_kv_pages_grouped_kernel(
   const int row_elems = num_kv_heads * head_dim;
   const int vec_per_token = row_elems >> 3;
   const int vec_per_head = head_dim >> 3;
-  const int pitch = row_elems * 2 + 16;  // bytes; the 16-byte skew keeps the transposed reads off one bank group
+  // A work item is a group of tokens x one of `parts` equal slices of the token row: smaller items, more CTAs per SM.
+  const int part_vecs = vec_per_token / parts;
+  const int pitch = part_vecs * 16 + 16;  // bytes; the 16-byte skew keeps the transposed reads off one bank group
   unsigned char* sK = fill_smem;
   unsigned char* sV = fill_smem + kGroupTokens * pitch;
   const long long num_groups = (num_tokens + kGroupTokens - 1) / kGroupTokens;
 
-  for (long long grp = blockIdx.x; grp < num_groups; grp += gridDim.x) {
+  for (long long item = blockIdx.x; item < num_groups * parts; item += gridDim.x) {
+    const long long grp = item / parts;
+    const int vec0 = (int)(item - grp * parts) * part_vecs;  // first 16-byte vector of this slice within a token row
     const long long t0 = grp * kGroupTokens;
     const int ntok = (int)min((long long)kGroupTokens, num_tokens - t0);
     __syncthreads();  // the previous group's shared data is no longer needed
@@ -157,8 +167,8 @@ __global__ void __launch_bounds__(256) fill_kv_pages_grouped_kernel(
 
     if (!s_any_wide) {
       // scattered path for this group (same stores as fill_kv_pages_kernel)
-      for (int v = threadIdx.x; v < ntok * vec_per_token; v += blockDim.x) {
-        const int i = v / vec_per_token, in_token = v - i * vec_per_token;
+      for (int v = threadIdx.x; v < ntok * part_vecs; v += blockDim.x) {
+        const int i = v / part_vecs, in_token = vec0 + v - i * part_vecs;
         const long long page = s_page[i];
         if (page < 0) continue;
         const int h = in_token / vec_per_head, c = in_token - h * vec_per_head, slot = s_slot[i];
@@ -177,29 +187,31 @@ __global__ void __launch_bounds__(256) fill_kv_pages_grouped_kernel(
       continue;
     }
 
-    // stage the group's K and V rows (coalesced 16-byte loads)
-    for (int v = threadIdx.x; v < ntok * vec_per_token; v += blockDim.x) {
-      const int i = v / vec_per_token, in_token = v - i * vec_per_token;
-      *reinterpret_cast<uint4*>(sK + i * pitch + in_token * 16) = new_keys[(t0 + i) * vec_per_token + in_token];
-      *reinterpret_cast<uint4*>(sV + i * pitch + in_token * 16) = new_values[(t0 + i) * vec_per_token + in_token];
+    // stage the group's K and V rows: coalesced 16-byte asynchronous copies, all in flight at once
+    for (int v = threadIdx.x; v < ntok * part_vecs; v += blockDim.x) {
+      const int i = v / part_vecs, in_part = v - i * part_vecs;
+      cp_async_16(sK + i * pitch + in_part * 16, new_keys + (t0 + i) * vec_per_token + vec0 + in_part);
+      cp_async_16(sV + i * pitch + in_part * 16, new_values + (t0 + i) * vec_per_token + vec0 + in_part);
     }
+    asm volatile("cp.async.wait_all;" ::: "memory");
     __syncthreads();
     // K: consecutive threads take consecutive tokens of one (head, chunk): 16-byte stores that are contiguous
     // in the pool wherever the slots are
-    for (int u = threadIdx.x; u < vec_per_token * kGroupTokens; u += blockDim.x) {
-      const int i = u & (kGroupTokens - 1), in_token = u >> 4;
+    for (int u = threadIdx.x; u < part_vecs * kGroupTokens; u += blockDim.x) {
+      const int i = u & (kGroupTokens - 1), in_part = u >> 4, in_token = vec0 + in_part;
       if (i >= ntok) continue;
       const long long page = s_page[i];
       if (page < 0) continue;
       const int h = in_token / vec_per_head, c = in_token - h * vec_per_head;
       const long long head_base = (page * num_kv_heads + h) * (long long)head_dim * tokens_per_page;
       *reinterpret_cast<uint4*>(k_pool + head_base + ((long long)c * tokens_per_page + s_slot[i]) * 8) =
-          *reinterpret_cast<const uint4*>(sK + i * pitch + in_token * 16);
+          *reinterpret_cast<const uint4*>(sK + i * pitch + in_part * 16);
     }
     // V: one thread per (head, d) row; a chunk of 8, 4 or 2 tokens becomes one 16-, 8- or 4-byte store
-    for (int e = threadIdx.x; e < row_elems; e += blockDim.x) {
+    for (int el = threadIdx.x; el < part_vecs * 8; el += blockDim.x) {
+      const int e = vec0 * 8 + el;
       const int h = e / head_dim, d = e - h * head_dim;
-      const unsigned char* col = sV + e * 2;
+      const unsigned char* col = sV + el * 2;
       int i = 0;
       while (i < ntok) {
         const int chunk = s_chunk[i];
@@ -232,10 +244,14 @@ int launch_fill(const FillArgs& a, cudaStream_t stream) {
   if (total_vecs == 0) return 0;
   // Enough tokens for runs to exist and rows that fit shared memory: the grouped kernel (it falls back
   // to scattered stores group by group).  V's 16-byte stores need TPP to be a multiple of 8.
-  const size_t grouped_smem = 2 * (size_t)kGroupTokens * ((size_t)a.num_kv_heads * a.head_dim * 2 + 16);
+  // The token row is cut into `parts` slices so that one work item stages about 32 KiB (several CTAs per SM).
+  const int vec_per_token = a.num_kv_heads * a.head_dim / 8;
+  int parts = 1;
+  while (parts < 8 && vec_per_token % (parts * 2) == 0 && vec_per_token / parts > 64) parts *= 2;
+  const size_t grouped_smem = 2 * (size_t)kGroupTokens * ((size_t)(vec_per_token / parts) * 16 + 16);
   if (a.num_tokens >= kGroupTokens && a.tokens_per_page % 8 == 0 && grouped_smem <= 160 * 1024) {
-    long long groups = (a.num_tokens + kGroupTokens - 1) / kGroupTokens;
-    const long long max_groups = 148LL * 16;
+    long long groups = (a.num_tokens + kGroupTokens - 1) / kGroupTokens * parts;
+    const long long max_groups = 148LL * 32;
     if (groups > max_groups) groups = max_groups;
     static bool configured[2][64] = {};
     int dev = 0;
@@ -253,12 +269,12 @@ int launch_fill(const FillArgs& a, cudaStream_t stream) {
       fill_kv_pages_grouped_kernel<true><<<(unsigned)groups, 256, grouped_smem, stream>>>(
           (const uint4*)a.new_keys, (const uint4*)a.new_values, (uint16_t*)a.k_pool, (uint16_t*)a.v_pool,
           a.slot_mapping, nullptr, nullptr, nullptr, a.num_tokens, a.num_seqs, a.num_kv_heads, a.head_dim,
-          a.tokens_per_page, a.num_pages, a.max_pages_per_seq);
+          a.tokens_per_page, a.num_pages, a.max_pages_per_seq, parts);
     else
       fill_kv_pages_grouped_kernel<false><<<(unsigned)groups, 256, grouped_smem, stream>>>(
           (const uint4*)a.new_keys, (const uint4*)a.new_values, (uint16_t*)a.k_pool, (uint16_t*)a.v_pool, nullptr,
           (const uint32_t*)a.page_table, a.write_positions, (const uint32_t*)a.query_to_seq_map, a.num_tokens,
-          a.num_seqs, a.num_kv_heads, a.head_dim, a.tokens_per_page, a.num_pages, a.max_pages_per_seq);
+          a.num_seqs, a.num_kv_heads, a.head_dim, a.tokens_per_page, a.num_pages, a.max_pages_per_seq, parts);
     return (int)cudaGetLastError();
   }
   long long blocks = (total_vecs + 255) / 256;
