@@ -4,7 +4,7 @@
 ``python bench.py --gpus N --steps K --warmup W`` prints ONE JSON line (rank 0).  A step is one pass
 of the operator over one batch of synthetic input already resident in HBM.  The default workload is
 the Llama-3-8B-shaped decode batch the headline metric (paged decode KV GB/s) is quoted on; other
-workloads (``--workload decode_70b | prefill_8b | fill``) cover the remaining configurations.
+workloads (``--workload decode_70b | prefill_8b | fill | fill_append``) cover the remaining configurations.
 
 ``--impl reference`` times the reference side of the comparison instead.  Proxy Attention Lab has no
 CPU implementation and its Metal kernels cannot run here, so that arm is the CPU oracle (the
