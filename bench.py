@@ -31,6 +31,16 @@ WORKLOADS = {
     # name: (kind, params)
     "decode_8b": dict(kind="decode", S=64, lo=1024, hi=8192, hq=32, hkv=8, d=128, tpp=16, partition_pages=0,
                       desc="Llama-3-8B decode: batch 64, context U[1024,8192], 32q/8kv heads, D=128, bf16, TPP=16, fused single pass"),
+    "decode_8b_append": dict(kind="decode", S=64, lo=1024, hi=8192, hq=32, hkv=8, d=128, tpp=16, partition_pages=0, append="fused",
+                             desc="Llama-3-8B decode step with the newest token appended in the same launch (paged_attention_decode_append): "
+                                  "batch 64, context U[1024,8192], 32q/8kv heads, D=128, bf16, TPP=16"),
+    "decode_8b_append_pair": dict(kind="decode", S=64, lo=1024, hi=8192, hq=32, hkv=8, d=128, tpp=16, partition_pages=0, append="pair",
+                                  desc="the same decode step as two calls, fill_kv_pages then paged_attention_decode: "
+                                       "batch 64, context U[1024,8192], 32q/8kv heads, D=128, bf16, TPP=16"),
+    "decode_small_append": dict(kind="decode", S=4, lo=64, hi=512, hq=8, hkv=2, d=128, tpp=16, partition_pages=0, append="fused",
+                                desc="latency case, newest token appended in the same launch: batch 4, context U[64,512], 8q/2kv heads, D=128, bf16, TPP=16"),
+    "decode_small_append_pair": dict(kind="decode", S=4, lo=64, hi=512, hq=8, hkv=2, d=128, tpp=16, partition_pages=0, append="pair",
+                                     desc="latency case as two calls, fill_kv_pages then paged_attention_decode: batch 4, context U[64,512], 8q/2kv heads, D=128, bf16, TPP=16"),
     "decode_70b": dict(kind="decode", S=8, lo=131072, hi=131072, hq=64, hkv=8, d=128, tpp=16, partition_pages=256,
                        desc="Llama-3-70B long decode: batch 8, context 131072, 64q/8kv heads, D=128, bf16, TPP=16, two-pass 256-page partitions"),
     "decode_70b_ctx": dict(kind="decode", S=8, lo=131072, hi=131072, hq=64, hkv=8, d=128, tpp=16, partition_pages=256, ctx_sharded=True,
@@ -392,7 +402,20 @@ def main():
             if world > 1:  # every rank must hold the same queries
                 dist.broadcast(data["q"], src=0)
 
+        append = cfg.get("append")
+        if append:
+            gen = torch.Generator(device=device).manual_seed(1234 + rank)
+            new_k = torch.randn((cfg["S"], data["k_pool"].shape[1], cfg["d"]), device=device, dtype=torch.bfloat16, generator=gen)
+            new_v = torch.randn_like(new_k)
+            new_k_host, new_v_host = new_k.cpu().pin_memory(), new_v.cpu().pin_memory()
+            last_pos = (data["lens"] - 1).to(torch.int32)
+            seq_ids = torch.arange(cfg["S"], device=device, dtype=torch.int32)
+
         def decode_call(q, table, lens):
+            if append == "fused":
+                return pal.paged_attention_decode_append(new_k, new_v, q, data["k_pool"], data["v_pool"], table, lens, partition_pages=pp)
+            if append == "pair":
+                pal.fill_kv_pages(new_k, new_v, data["k_pool"], data["v_pool"], table, last_pos, seq_ids)
             if not ctx:
                 return pal.paged_attention_decode(q, data["k_pool"], data["v_pool"], table, lens, partition_pages=pp)
             m, l, acc = pal.paged_attention_decode_partials(q, data["k_pool"], data["v_pool"], table, lens, partition_pages=pp)
@@ -412,14 +435,21 @@ def main():
             q_dev.copy_(data["q_host"], non_blocking=True)
             t_dev.copy_(data["table_host"], non_blocking=True)
             l_dev.copy_(data["lens_host"], non_blocking=True)
+            if append:
+                new_k.copy_(new_k_host, non_blocking=True)
+                new_v.copy_(new_v_host, non_blocking=True)
             out = decode_call(q_dev, t_dev, l_dev)
             out_host.copy_(out, non_blocking=True)
 
         h2d = data["q_host"].numel() * 2 + data["table_host"].numel() * 4 + data["lens_host"].numel() * 4
         d2h = out_host.numel() * 2
+        if append:
+            h2d += 2 * new_k_host.numel() * 2
         units_per_step, alg_per_step = data["kv_bytes"], data["alg_bytes"]
         to_value = lambda units, sec: units / sec / 1e9
         launches_per_step = (3 if ctx else 2) if pp else 1
+        if append == "pair":
+            launches_per_step += 1
         bound, peak = "hbm", peaks["hbm"]
         achieved_of = lambda sec: alg_per_step / sec / 1e9
         roof_unit = "GB/s"

@@ -121,6 +121,22 @@ int pal_paged_attention_decode_static(const void* queries, const void* k_pool, c
                                       int tokens_per_page, int64_t num_pages, int max_pages_per_seq,
                                       float scale, int dtype, int partition_pages, void* stream);
 
+/* Fused "append + attend": the decode step a serving loop runs as fill_kv_pages for each sequence's newest
+ * token followed by paged_attention_decode (src/proxy_attention_lab/ops.py:33-84 and :133-176 called back to
+ * back; the reference has no fused form).  new_keys / new_values [S, Hkv, D] hold the K and V of the token at
+ * position sequence_lengths[s] - 1 (the lengths already count it).  In one launch the kernel stores them into
+ * page page_table[s, (L-1)/TPP], slot (L-1)%TPP of both pools - bit for bit what pal_fill_kv_pages would write -
+ * and attends over all L tokens, taking the newest token from new_keys / new_values rather than from the pool.
+ * Sequences of length <= 0, or whose last page lies beyond max_pages_per_seq, append nothing; a page id
+ * >= num_pages is not written.  Everything else as pal_paged_attention_decode (same workspace rule). */
+int pal_paged_attention_decode_append(const void* new_keys, const void* new_values, const void* queries,
+                                      void* k_pool, void* v_pool, const void* page_table,
+                                      const int32_t* sequence_lengths, void* out, int num_seqs,
+                                      int num_q_heads, int num_kv_heads, int head_dim, int tokens_per_page,
+                                      int64_t num_pages, int max_pages_per_seq, float scale, int dtype,
+                                      int partition_pages, void* workspace, size_t workspace_bytes,
+                                      void* stream);
+
 /* First half of the two-pass decode, for callers that merge partials themselves (for example
  * across GPUs that each hold a slice of every sequence's context).  Runs the split-KV pass over
  * the pages this pool holds and merges its own partitions, but does not normalise: writes

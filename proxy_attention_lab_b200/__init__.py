@@ -14,6 +14,7 @@ from .ops import (  # noqa: F401
     lse_combine,
     paged_attention,
     paged_attention_decode,
+    paged_attention_decode_append,
     paged_attention_decode_partials,
     paged_attention_prefill,
 )
@@ -27,6 +28,7 @@ __all__ = [
     "lse_combine",
     "paged_attention",
     "paged_attention_decode",
+    "paged_attention_decode_append",
     "paged_attention_decode_partials",
     "paged_attention_prefill",
 ]

@@ -243,6 +243,43 @@ int pal_paged_attention_decode(const void* queries, const void* k_pool, const vo
   return decode_common(a, stream, "paged_attention_decode");
 }
 
+int pal_paged_attention_decode_append(const void* new_keys, const void* new_values, const void* queries, void* k_pool,
+                                      void* v_pool, const void* page_table, const int32_t* sequence_lengths, void* out,
+                                      int num_seqs, int num_q_heads, int num_kv_heads, int head_dim, int tokens_per_page,
+                                      int64_t num_pages, int max_pages_per_seq, float scale, int dtype,
+                                      int partition_pages, void* workspace, size_t workspace_bytes, void* stream) {
+  DecodeArgs a{};
+  a.queries = queries;
+  a.k_pool = k_pool;
+  a.v_pool = v_pool;
+  a.new_keys = new_keys;
+  a.new_values = new_values;
+  a.page_table = static_cast<const uint32_t*>(page_table);
+  a.sequence_lengths = sequence_lengths;
+  a.out = out;
+  a.num_seqs = num_seqs;
+  a.num_q_heads = num_q_heads;
+  a.num_kv_heads = num_kv_heads;
+  a.head_dim = head_dim;
+  a.tokens_per_page = tokens_per_page;
+  a.num_pages = num_pages;
+  a.max_pages_per_seq = max_pages_per_seq;
+  a.scale = scale;
+  a.dtype = dtype;
+  a.partition_pages = partition_pages;
+  a.workspace = workspace;
+  a.workspace_bytes = workspace_bytes;
+  if (num_seqs > 0 && (!out || !new_keys || !new_values)) {
+    set_error("paged_attention_decode_append: out, new_keys or new_values is null");
+    return PAL_ERR_BAD_ARG;
+  }
+  if (!aligned16(new_keys) || !aligned16(new_values)) {
+    set_error("paged_attention_decode_append: new_keys and new_values must be 16-byte aligned");
+    return PAL_ERR_BAD_ARG;
+  }
+  return decode_common(a, stream, "paged_attention_decode_append");
+}
+
 int pal_paged_attention_decode_partials(const void* queries, const void* k_pool, const void* v_pool,
                                         const void* page_table, const int32_t* sequence_lengths, float* m_out,
                                         float* l_out, float* acc_out, int num_seqs, int num_q_heads,

@@ -46,6 +46,8 @@ struct DecodeParams {
   const void* q;
   const void* k_pool;
   const void* v_pool;
+  const void* new_k;  // append form only: [S, Hkv, D] K and V of each sequence's last token
+  const void* new_v;
   const uint32_t* page_table;
   const int32_t* seq_lens;
   void* out;
@@ -111,7 +113,7 @@ __device__ __forceinline__ void page_range(const DecodeParams& p, int len, int p
   }
 }
 
-template <typename T, int D, int TPP, bool SPLIT>
+template <typename T, int D, int TPP, bool SPLIT, bool APPEND>
 __global__ void __launch_bounds__(kDecodeThreads, 2) paged_decode_kernel(const DecodeParams p) {
   using SM = DecodeSmem<D, TPP>;
   using MMA = Mma16816<T>;
@@ -275,6 +277,28 @@ __global__ void __launch_bounds__(kDecodeThreads, 2) paged_decode_kernel(const D
         qf[ks][1] = valid ? qrow[ks * 8 + 4 + t] : 0u;
       }
     }
+    // Append form: the sequence's last token (position len - 1) is not in the pool yet.  The warp that owns its page
+    // fetches the token's K and V rows here, and when the page lands in shared memory it overwrites the token's slot
+    // there before using it; the item of the first head group also stores the rows into the pool.
+    int last_j = -1, last_slot = 0;
+    uint4 app_k = make_uint4(0u, 0u, 0u, 0u), app_v = make_uint4(0u, 0u, 0u, 0u);
+    long long app_block = -1;  // byte offset of the (page, kv head) block in the pools, -1 = do not store
+    if (APPEND && len > 0) {
+      const int last_page = (len - 1) / TPP;
+      if (last_page >= pb && last_page < pe && ((last_page - pb) & (kConsumerWarps - 1)) == warp) {
+        last_j = last_page - pb;
+        last_slot = (len - 1) - last_page * TPP;
+        const size_t row = ((size_t)c.seq * p.num_kv_heads + c.kvh) * D;
+        if (lane < D / 8) {
+          app_k = reinterpret_cast<const uint4*>(static_cast<const T*>(p.new_k) + row)[lane];
+          app_v = reinterpret_cast<const uint4*>(static_cast<const T*>(p.new_v) + row)[lane];
+        }
+        if (c.hg == 0) {
+          const uint32_t pid = p.page_table[(size_t)c.seq * p.max_pages_per_seq + last_page];
+          if ((long long)pid < p.num_pages) app_block = ((long long)pid * p.num_kv_heads + c.kvh) * SM::kBlockBytes;
+        }
+      }
+    }
     float m_run[2] = {-INFINITY, -INFINITY};
     float l_run[2] = {0.f, 0.f};
     float o[MTILES][4];
@@ -292,6 +316,34 @@ __global__ void __launch_bounds__(kDecodeThreads, 2) paged_decode_kernel(const D
         __syncwarp();
         if (lane == 0) mbar_arrive(&empty_bar[stage]);
         continue;
+      }
+      if (APPEND && j == last_j) {
+        unsigned char* ks = stages + stage * SM::kStageBytes;
+        unsigned char* vs = ks + SM::kBlockBytes;
+        if (lane < D / 8) {
+          // K block [D/8][TPP][8]: chunk `lane` of the token; V block [D][TPP]: elements 8 lane .. 8 lane + 7
+          const int k_off = lane * (TPP * 16) + last_slot * 16;
+          *reinterpret_cast<uint4*>(ks + k_off) = app_k;
+          const uint32_t w[4] = {app_v.x, app_v.y, app_v.z, app_v.w};
+#pragma unroll
+          for (int e = 0; e < 8; ++e) {
+            const uint16_t val = (uint16_t)(w[e >> 1] >> ((e & 1) * 16));
+            *reinterpret_cast<uint16_t*>(vs + (lane * 8 + e) * (TPP * 2) + last_slot * 2) = val;
+          }
+          if (app_block >= 0) {
+            unsigned char* kg = static_cast<unsigned char*>(const_cast<void*>(p.k_pool)) + app_block;
+            unsigned char* vg = static_cast<unsigned char*>(const_cast<void*>(p.v_pool)) + app_block;
+            *reinterpret_cast<uint4*>(kg + k_off) = app_k;
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+              const uint16_t val = (uint16_t)(w[e >> 1] >> ((e & 1) * 16));
+              *reinterpret_cast<uint16_t*>(vg + (lane * 8 + e) * (TPP * 2) + last_slot * 2) = val;
+            }
+          }
+        }
+        // the stage is refilled later by an asynchronous copy: order these generic writes before it
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        __syncwarp();
       }
       const uint32_t kb = smem_u32(stages + stage * SM::kStageBytes);
       const uint32_t vb = kb + SM::kBlockBytes;
@@ -513,11 +565,11 @@ __global__ void __launch_bounds__(128) lse_combine_kernel(const float* __restric
   }
 }
 
-template <typename T, int D, int TPP, bool SPLIT>
+template <typename T, int D, int TPP, bool SPLIT, bool APPEND>
 int launch_decode_inst(const DecodeParams& p, int num_sms, cudaStream_t stream) {
   using SM = DecodeSmem<D, TPP>;
   static_assert(SM::kTotalBytes <= 227 * 1024, "decode shared memory exceeds the per-CTA limit");
-  auto kern = paged_decode_kernel<T, D, TPP, SPLIT>;
+  auto kern = paged_decode_kernel<T, D, TPP, SPLIT, APPEND>;
   static bool configured[64] = {};
   int dev = 0;
   cudaGetDevice(&dev);
@@ -536,8 +588,10 @@ int launch_decode_inst(const DecodeParams& p, int num_sms, cudaStream_t stream) 
 
 template <typename T, bool SPLIT>
 int dispatch_shape(const DecodeParams& p, int head_dim, int tpp, int num_sms, cudaStream_t stream) {
-#define PAL_DECODE_CASE(DD, TT) \
-  if (head_dim == DD && tpp == TT) return launch_decode_inst<T, DD, TT, SPLIT>(p, num_sms, stream);
+#define PAL_DECODE_CASE(DD, TT)                                                                        \
+  if (head_dim == DD && tpp == TT)                                                                     \
+    return p.new_k ? launch_decode_inst<T, DD, TT, SPLIT, true>(p, num_sms, stream)                    \
+                   : launch_decode_inst<T, DD, TT, SPLIT, false>(p, num_sms, stream);
   PAL_DECODE_CASE(32, 16)
   PAL_DECODE_CASE(64, 16)
   PAL_DECODE_CASE(80, 16)
@@ -627,6 +681,8 @@ int launch_decode(const DecodeArgs& a, cudaStream_t stream) {
   p.q = a.queries;
   p.k_pool = a.k_pool;
   p.v_pool = a.v_pool;
+  p.new_k = a.new_keys;
+  p.new_v = a.new_values;
   p.page_table = a.page_table;
   p.seq_lens = a.sequence_lengths;
   p.out = a.out;

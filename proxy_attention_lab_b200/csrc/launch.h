@@ -33,6 +33,8 @@ struct DecodeArgs {
   const void* queries;
   const void* k_pool;
   const void* v_pool;
+  const void* new_keys = nullptr;    // both set = append form: the pools are written as well (see decode.cu)
+  const void* new_values = nullptr;
   const uint32_t* page_table;
   const int32_t* sequence_lengths;
   void* out;            // [S, Hq, D] in the query dtype (null when only the triple is wanted)

@@ -234,6 +234,39 @@ def paged_attention_decode(queries, k_cache_pool, v_cache_pool, page_table, sequ
     return out
 
 
+def paged_attention_decode_append(new_keys, new_values, queries, k_cache_pool, v_cache_pool, page_table, sequence_lengths, *,
+                                  stream=None, partition_pages=None, scale=None):
+    """``fill_kv_pages`` of each sequence's newest token and ``paged_attention_decode`` in one launch.
+
+    ``new_keys / new_values [S, Hkv, D]`` belong to position ``sequence_lengths[s] - 1`` (the lengths already
+    count the new token).  The pools are updated in place exactly as ``fill_kv_pages`` would; returns the
+    attention output ``[S, Hq, D]``.
+    """
+    S, hq, hkv, d, tpp, num_pages = _decode_shapes(queries, k_cache_pool, v_cache_pool, page_table, sequence_lengths)
+    for name, t in (("new_keys", new_keys), ("new_values", new_values)):
+        _need_cuda(name, t)
+        if tuple(t.shape) != (S, hkv, d) or t.dtype != queries.dtype:
+            raise ValueError(f"{name} must be [{S}, {hkv}, {d}] of {queries.dtype}")
+    dev = queries.device
+    out = torch.empty((S, hq, d), dtype=queries.dtype, device=dev)
+    if S == 0:
+        return out
+    q = _contig(queries)
+    nk, nv = _contig(new_keys), _contig(new_values)
+    pt = _index32("page_table", page_table)
+    lens = _index32("sequence_lengths", sequence_lengths)
+    pp = _lib.PAL_DECODE_AUTO if partition_pages is None else int(partition_pages)
+    with torch.cuda.device(dev):
+        nbytes = lib.pal_decode_workspace_bytes(S, hq, hkv, d, tpp, pt.shape[1], pp)
+        ws = _workspace(nbytes, dev)
+        rc = lib.pal_paged_attention_decode_append(nk.data_ptr(), nv.data_ptr(), q.data_ptr(), _ptr(k_cache_pool),
+                                                   _ptr(v_cache_pool), _ptr(pt), lens.data_ptr(), out.data_ptr(), S, hq, hkv, d,
+                                                   tpp, num_pages, pt.shape[1], 0.0 if scale is None else float(scale),
+                                                   _dtype_code(q.dtype), pp, ws.data_ptr(), ws.numel(), _stream_ptr(stream, dev))
+        _lib.check(rc)
+    return out
+
+
 def paged_attention_decode_partials(queries, k_cache_pool, v_cache_pool, page_table, sequence_lengths, *,
                                     partition_pages: int = 256, scale=None, stream=None):
     """Split-KV pass without the final normalisation: returns fp32 ``(m [S,Hq], l [S,Hq], acc [S,Hq,D])``.
