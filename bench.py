@@ -50,6 +50,9 @@ WORKLOADS = {
                        desc="Llama-3-8B chunked causal prefill: 8 x 2048 new tokens, history U[0,4096], 32q/8kv heads, D=128, bf16, TPP=16"),
     "prefill_small": dict(kind="prefill", S=2, n=1024, hlo=0, hhi=2048, hq=32, hkv=8, d=128, tpp=16,
                           desc="reduced chunked prefill for profiler captures: 2 x 1024 new tokens, history U[0,2048], 32q/8kv heads, D=128, bf16, TPP=16"),
+    "prefill_ragged": dict(kind="prefill", S=8, n=2048, nlo=128, hlo=0, hhi=4096, hq=32, hkv=8, d=128, tpp=16,
+                           desc="ragged chunked causal prefill (paged_attention_prefill_ragged): 8 sequences with U[128,2048] new tokens each, "
+                                "history U[0,4096], 32q/8kv heads, D=128, bf16, TPP=16"),
     "fill": dict(kind="fill", S=64, n=512, hkv=8, d=128, tpp=16, pages=65536,
                  desc="fill_kv_pages: 64 x 512 tokens, 8 kv heads, D=128, bf16, TPP=16, 65536-page pool, random free slots"),
     "fill_append_small": dict(kind="fill", S=48, n=1024, hkv=8, d=128, tpp=16, pages=16384, append=True, hhi=4096,
@@ -192,10 +195,16 @@ def build_prefill(cfg, device, seed, seqs=None):
         off += m
     gen = torch.Generator(device=device).manual_seed(seed + 2)
     mk = lambda *shape: torch.randn(shape, device=device, dtype=torch.bfloat16, generator=gen)
-    data = dict(k_pool=mk(P, hkv, d // 8, tpp, 8), v_pool=mk(P, hkv, d, tpp), q=mk(S * n, hq, d), k=mk(S * n, hkv, d), v=mk(S * n, hkv, d),
+    # ragged workloads draw every sequence's number of new tokens from U[nlo, n]
+    counts = make_lengths(seed + 5, cfg["S"], cfg["nlo"], n)[idx] if "nlo" in cfg else torch.full((S,), n, dtype=torch.int64)
+    T = int(counts.sum())
+    data = dict(k_pool=mk(P, hkv, d // 8, tpp, 8), v_pool=mk(P, hkv, d, tpp), q=mk(T, hq, d), k=mk(T, hkv, d), v=mk(T, hkv, d),
                 table=table.to(device), hist=hist.to(torch.int32).to(device))
-    data["flops"] = 4 * hq * d * sum(n * int(h) + n * (n + 1) // 2 for h in hist)
-    data["tokens"] = S * n
+    if "nlo" in cfg:
+        data["cu"] = torch.cat([torch.zeros(1, dtype=torch.int64), counts.cumsum(0)]).to(torch.int32).to(device)
+        data["max_new"] = int(counts.max())
+    data["flops"] = 4 * hq * d * sum(int(c) * int(h) + int(c) * (int(c) + 1) // 2 for c, h in zip(counts, hist))
+    data["tokens"] = T
     data["hist_cpu"] = hist
     return data
 
@@ -460,25 +469,30 @@ def main():
             from proxy_attention_lab_b200.sharding import partition_sequences
 
             hist_all = make_lengths(0, cfg["S"], cfg["hlo"], cfg["hhi"])
-            work = [cfg["n"] * int(h) + cfg["n"] * (cfg["n"] + 1) // 2 for h in hist_all]
+            n_all = make_lengths(5, cfg["S"], cfg["nlo"], cfg["n"]).tolist() if "nlo" in cfg else [cfg["n"]] * cfg["S"]
+            work = [n * int(h) + n * (n + 1) // 2 for n, h in zip(n_all, hist_all)]
             seqs = partition_sequences(work, world)[rank] or [rank % cfg["S"]]
             scaling = "strong"
             extra_cfg["parallelism"] = f"sequence sharded x{world}, no collective"
         data = build_prefill(cfg, device, seed=0, seqs=seqs)
 
-        def step():
-            return pal.paged_attention_prefill(data["q"], data["k"], data["v"], data["k_pool"], data["v_pool"], data["table"], data["hist"],
-                                               impl=args.prefill_impl)
+        def prefill_call(q, k, v, table, hist, cu=None):
+            if cu is None:
+                return pal.paged_attention_prefill(q, k, v, data["k_pool"], data["v_pool"], table, hist, impl=args.prefill_impl)
+            return pal.paged_attention_prefill_ragged(q, k, v, data["k_pool"], data["v_pool"], table, hist, cu,
+                                                      max_new_tokens=data["max_new"], impl=args.prefill_impl)
 
-        host = {k: data[k].cpu().pin_memory() for k in ("q", "k", "v", "table", "hist")}
+        def step():
+            return prefill_call(data["q"], data["k"], data["v"], data["table"], data["hist"], data.get("cu"))
+
+        host = {k: data[k].cpu().pin_memory() for k in ("q", "k", "v", "table", "hist") + (("cu",) if "cu" in data else ())}
         devb = {k: torch.empty_like(data[k]) for k in host}
         out_host = torch.empty((data["tokens"] * cfg["hq"], cfg["d"]), dtype=torch.bfloat16).pin_memory()
 
         def e2e_step():
             for k in host:
                 devb[k].copy_(host[k], non_blocking=True)
-            out = pal.paged_attention_prefill(devb["q"], devb["k"], devb["v"], data["k_pool"], data["v_pool"], devb["table"], devb["hist"],
-                                              impl=args.prefill_impl)
+            out = prefill_call(devb["q"], devb["k"], devb["v"], devb["table"], devb["hist"], devb.get("cu"))
             out_host.copy_(out, non_blocking=True)
 
         h2d = sum(t.numel() * t.element_size() for t in host.values())

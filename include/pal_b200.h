@@ -180,6 +180,22 @@ int pal_paged_attention_prefill(const void* q_prompt, const void* k_prompt, cons
                                 float scale, int dtype, int impl, void* workspace,
                                 size_t workspace_bytes, void* stream);
 
+/* Ragged form of pal_paged_attention_prefill: sequence s brings cu_seqlens[s+1] - cu_seqlens[s] new tokens (any
+ * count, zero included), stored back to back: q_prompt [total_tokens, Hq, D], k_prompt / v_prompt
+ * [total_tokens, Hkv, D], out [total_tokens*Hq, D]; cu_seqlens is a device array of num_seqs + 1 int32 row offsets
+ * with cu_seqlens[0] = 0 and cu_seqlens[num_seqs] = total_tokens.  max_new_tokens is the largest count (it sizes
+ * the grid; a smaller value than the truth leaves the tail of long sequences unwritten).  A batch that mixes prefill
+ * chunks with single-token decode steps is the case count = 1.  No counterpart in the reference, which derives one
+ * uniform count as q.shape(0) / num_sequences (src/pal_core/src/paged_attention_prefill_primitive.cpp:115-116).
+ * With equal counts the result is bit-identical to pal_paged_attention_prefill. */
+int pal_paged_attention_prefill_ragged(const void* q_prompt, const void* k_prompt, const void* v_prompt,
+                                       const void* k_pool, const void* v_pool, const void* page_table,
+                                       const int32_t* history_lens, const int32_t* cu_seqlens, void* out,
+                                       int num_seqs, int64_t total_tokens, int max_new_tokens, int num_q_heads,
+                                       int num_kv_heads, int head_dim, int tokens_per_page, int64_t num_pages,
+                                       int max_pages_per_seq, float scale, int dtype, int impl, void* workspace,
+                                       size_t workspace_bytes, void* stream);
+
 /* Reads (with a blocking copy on `stream`) the status word the kernels of the last call that
  * used `workspace` left there: PAL_OK, or PAL_ERR_TIMEOUT when a bounded device-side wait gave
  * up.  Optional; intended for tests and debugging. */

@@ -32,5 +32,6 @@ from .attention import (  # noqa: F401
     decode_partials_oracle,
     lse_combine_oracle,
     prefill_oracle,
+    prefill_ragged_oracle,
 )
 from .fill import fill_kv_pages_oracle, slots_from_page_table  # noqa: F401

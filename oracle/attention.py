@@ -133,3 +133,19 @@ def prefill_oracle(q_prompt, k_prompt, v_prompt, k_pool, v_pool, page_table, con
             p = torch.softmax(scores, dim=-1)
             out[s, :, h * g:(h + 1) * g, :] = torch.matmul(p, v[:, h, :]).permute(1, 0, 2)
     return out.reshape(S * n * hq, d)
+
+
+def prefill_ragged_oracle(q_prompt, k_prompt, v_prompt, k_pool, v_pool, page_table, context_lens, cu_seqlens, scale=None):
+    """fp32 ``[T*Hq, D]`` for sequences with different numbers of new tokens: sequence ``s`` owns rows
+    ``cu_seqlens[s] .. cu_seqlens[s+1] - 1`` and is computed exactly as a one-sequence uniform batch
+    (the per-row semantics of ``paged_attention_prefill.h.metal:136-165,243-266`` do not depend on the other sequences)."""
+    hq, d = q_prompt.shape[1], q_prompt.shape[2]
+    out = torch.zeros((q_prompt.shape[0], hq, d), dtype=torch.float32)
+    for s in range(context_lens.shape[0]):
+        a, b = int(cu_seqlens[s]), int(cu_seqlens[s + 1])
+        if b <= a:
+            continue
+        out[a:b] = prefill_oracle(q_prompt[a:b], k_prompt[a:b], v_prompt[a:b], k_pool, v_pool, page_table[s:s + 1],
+                                  context_lens[s:s + 1], scale=scale).reshape(b - a, hq, d)
+    return out.reshape(-1, d)
+

@@ -17,6 +17,7 @@ from .ops import (  # noqa: F401
     paged_attention_decode_append,
     paged_attention_decode_partials,
     paged_attention_prefill,
+    paged_attention_prefill_ragged,
 )
 
 __all__ = [
@@ -31,4 +32,5 @@ __all__ = [
     "paged_attention_decode_append",
     "paged_attention_decode_partials",
     "paged_attention_prefill",
+    "paged_attention_prefill_ragged",
 ]

@@ -61,6 +61,10 @@ SIGNATURES = {
         c_int,
         [_P, _P, _P, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int, c_int64, c_int, c_float, c_int, c_int, _P, c_size_t, _P],
     ),
+    "pal_paged_attention_prefill_ragged": (
+        c_int,
+        [_P, _P, _P, _P, _P, _P, _P, _P, _P, c_int, c_int64, c_int, c_int, c_int, c_int, c_int, c_int64, c_int, c_float, c_int, c_int, _P, c_size_t, _P],
+    ),
     "pal_check_status": (c_int, [_P, _P]),
 }
 

@@ -346,13 +346,13 @@ size_t pal_prefill_workspace_bytes(int num_seqs, int tokens_per_seq, int num_q_h
   return sizeof(WorkspaceHeader);
 }
 
-int pal_paged_attention_prefill(const void* q_prompt, const void* k_prompt, const void* v_prompt,
-                                const void* k_pool, const void* v_pool, const void* page_table,
-                                const int32_t* history_lens, void* out, int num_seqs, int tokens_per_seq,
-                                int num_q_heads, int num_kv_heads, int head_dim, int tokens_per_page,
-                                int64_t num_pages, int max_pages_per_seq, float scale, int dtype, int impl,
-                                void* workspace, size_t workspace_bytes, void* stream) {
-  const char* what = "paged_attention_prefill";
+// tokens_per_seq is the uniform count, or with cu_seqlens (ragged form) the longest sequence's count
+static int prefill_common(const char* what, const void* q_prompt, const void* k_prompt, const void* v_prompt,
+                          const void* k_pool, const void* v_pool, const void* page_table, const int32_t* history_lens,
+                          const int32_t* cu_seqlens, int64_t total_tokens, void* out, int num_seqs, int tokens_per_seq,
+                          int num_q_heads, int num_kv_heads, int head_dim, int tokens_per_page, int64_t num_pages,
+                          int max_pages_per_seq, float scale, int dtype, int impl, void* workspace,
+                          size_t workspace_bytes, void* stream) {
   if (!check_dtype(dtype, what)) return PAL_ERR_UNSUPPORTED;
   int rc = check_heads(what, num_q_heads, num_kv_heads, head_dim, tokens_per_page);
   if (rc != PAL_OK) return rc;
@@ -382,6 +382,8 @@ int pal_paged_attention_prefill(const void* q_prompt, const void* k_prompt, cons
   a.v_pool = v_pool;
   a.page_table = static_cast<const uint32_t*>(page_table);
   a.history_lens = history_lens;
+  a.cu_seqlens = cu_seqlens;
+  a.total_tokens = total_tokens;
   a.out = out;
   a.num_seqs = num_seqs;
   a.tokens_per_seq = tokens_per_seq;
@@ -408,6 +410,40 @@ int pal_paged_attention_prefill(const void* q_prompt, const void* k_prompt, cons
   const bool use_tc = impl == 2 || (impl == 0 && tc_ok && tokens_per_seq >= 64);
   return cuda_rc(use_tc ? launch_prefill_tcgen05(a, (cudaStream_t)stream) : launch_prefill_mma(a, (cudaStream_t)stream),
                  what);
+}
+
+int pal_paged_attention_prefill(const void* q_prompt, const void* k_prompt, const void* v_prompt,
+                                const void* k_pool, const void* v_pool, const void* page_table,
+                                const int32_t* history_lens, void* out, int num_seqs, int tokens_per_seq,
+                                int num_q_heads, int num_kv_heads, int head_dim, int tokens_per_page,
+                                int64_t num_pages, int max_pages_per_seq, float scale, int dtype, int impl,
+                                void* workspace, size_t workspace_bytes, void* stream) {
+  return prefill_common("paged_attention_prefill", q_prompt, k_prompt, v_prompt, k_pool, v_pool, page_table,
+                        history_lens, nullptr, (int64_t)num_seqs * tokens_per_seq, out, num_seqs, tokens_per_seq,
+                        num_q_heads, num_kv_heads, head_dim, tokens_per_page, num_pages, max_pages_per_seq, scale, dtype,
+                        impl, workspace, workspace_bytes, stream);
+}
+
+int pal_paged_attention_prefill_ragged(const void* q_prompt, const void* k_prompt, const void* v_prompt,
+                                       const void* k_pool, const void* v_pool, const void* page_table,
+                                       const int32_t* history_lens, const int32_t* cu_seqlens, void* out,
+                                       int num_seqs, int64_t total_tokens, int max_new_tokens, int num_q_heads,
+                                       int num_kv_heads, int head_dim, int tokens_per_page, int64_t num_pages,
+                                       int max_pages_per_seq, float scale, int dtype, int impl, void* workspace,
+                                       size_t workspace_bytes, void* stream) {
+  const char* what = "paged_attention_prefill_ragged";
+  if (total_tokens < 0 || total_tokens > 0x7fffffffLL) {
+    set_error("%s: total_tokens must be in [0, 2^31)", what);
+    return PAL_ERR_BAD_ARG;
+  }
+  if (num_seqs > 0 && total_tokens > 0 && max_new_tokens > 0 && !cu_seqlens) {
+    set_error("%s: cu_seqlens is null", what);
+    return PAL_ERR_BAD_ARG;
+  }
+  if (total_tokens == 0) return num_seqs < 0 ? PAL_ERR_BAD_ARG : PAL_OK;
+  return prefill_common(what, q_prompt, k_prompt, v_prompt, k_pool, v_pool, page_table, history_lens, cu_seqlens,
+                        total_tokens, out, num_seqs, max_new_tokens, num_q_heads, num_kv_heads, head_dim, tokens_per_page,
+                        num_pages, max_pages_per_seq, scale, dtype, impl, workspace, workspace_bytes, stream);
 }
 
 int pal_check_status(const void* workspace, void* stream) {

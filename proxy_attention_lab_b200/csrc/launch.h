@@ -63,6 +63,8 @@ struct PrefillArgs {
   const void* v_pool;
   const uint32_t* page_table;
   const int32_t* history_lens;
+  const int32_t* cu_seqlens = nullptr;  // ragged form: [S + 1] row offsets; tokens_per_seq is then the longest sequence
+  long long total_tokens = 0;           // ragged form: rows of q_prompt / k_prompt / v_prompt
   void* out;
   int num_seqs;
   int tokens_per_seq;

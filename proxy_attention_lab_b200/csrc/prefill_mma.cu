@@ -31,6 +31,7 @@ struct PrefillParams {
   const void* v_pool;
   const uint32_t* page_table;
   const int32_t* hist_lens;
+  const int32_t* cu_seqlens;  // ragged batches: first row of each sequence in q / k_new / v_new / out; null = uniform n_new
   void* out;
   int num_seqs, n_new, num_q_heads, num_kv_heads, group, max_pages_per_seq;
   long long num_pages;
@@ -59,7 +60,9 @@ __global__ void __launch_bounds__(kPrefillThreads) prefill_mma_kernel(const Pref
   const int h = blockIdx.y;
   const int s = blockIdx.z;
   const int kvh = h / p.group;
-  const int N = p.n_new;
+  const int N = p.cu_seqlens ? p.cu_seqlens[s + 1] - p.cu_seqlens[s] : p.n_new;
+  const size_t row0 = p.cu_seqlens ? (size_t)p.cu_seqlens[s] : (size_t)s * N;  // the sequence's first row
+  if (q0 >= N) return;  // ragged: the grid is sized for the longest sequence
   int H = p.hist_lens[s];
   if (H < 0) H = 0;
   if (p.num_pages <= 0) H = 0;
@@ -79,7 +82,7 @@ __global__ void __launch_bounds__(kPrefillThreads) prefill_mma_kernel(const Pref
     const int row = v / VEC_PER_ROW, cv = v - row * VEC_PER_ROW;
     uint4 val = make_uint4(0, 0, 0, 0);
     if (q0 + row < N)
-      val = *reinterpret_cast<const uint4*>(qg + (((size_t)s * N + q0 + row) * p.num_q_heads + h) * D + cv * 8);
+      val = *reinterpret_cast<const uint4*>(qg + ((row0 + q0 + row) * p.num_q_heads + h) * D + cv * 8);
     *reinterpret_cast<uint4*>(sQ + row * DP + cv * 8) = val;
   }
 
@@ -139,7 +142,7 @@ __global__ void __launch_bounds__(kPrefillThreads) prefill_mma_kernel(const Pref
         const int row = v / VEC_PER_ROW, cv = v - row * VEC_PER_ROW;
         uint4 kk = make_uint4(0, 0, 0, 0), vv = make_uint4(0, 0, 0, 0);
         if (j0 + row < N) {
-          const size_t off = (((size_t)s * N + j0 + row) * p.num_kv_heads + kvh) * D + cv * 8;
+          const size_t off = ((row0 + j0 + row) * p.num_kv_heads + kvh) * D + cv * 8;
           kk = *reinterpret_cast<const uint4*>(kg + off);
           vv = *reinterpret_cast<const uint4*>(vg + off);
         }
@@ -276,7 +279,7 @@ __global__ void __launch_bounds__(kPrefillThreads) prefill_mma_kernel(const Pref
     const int qi = rr ? i_hi : i_lo;
     if (qi >= N) continue;
     const float inv = l_run[rr] > 0.f ? 1.f / l_run[rr] : 0.f;
-    uint32_t* orow = reinterpret_cast<uint32_t*>(outp + (((size_t)s * N + qi) * p.num_q_heads + h) * D);
+    uint32_t* orow = reinterpret_cast<uint32_t*>(outp + ((row0 + qi) * p.num_q_heads + h) * D);
 #pragma unroll
     for (int nd = 0; nd < NDT; ++nd)
       orow[nd * 4 + t] = MMA::pack(o[nd][2 * rr] * inv, o[nd][2 * rr + 1] * inv);
@@ -333,6 +336,7 @@ int launch_prefill_mma(const PrefillArgs& a, cudaStream_t stream) {
   p.v_pool = a.v_pool;
   p.page_table = a.page_table;
   p.hist_lens = a.history_lens;
+  p.cu_seqlens = a.cu_seqlens;
   p.out = a.out;
   p.num_seqs = a.num_seqs;
   p.n_new = a.tokens_per_seq;

@@ -63,6 +63,7 @@ struct TcParams {
   const void* k_pool;
   const uint32_t* page_table;
   const int32_t* hist_lens;
+  const int32_t* cu_seqlens;  // ragged batches: first row of each sequence; null = every sequence has n_new rows
   void* out;
   unsigned int* status;
   unsigned int* trace;  // progress markers in host-visible memory; only used by builds with PAL_TC_TRACE
@@ -359,7 +360,13 @@ __global__ void __launch_bounds__(64 + 128 * NQ, 1)
   const int h0 = blockIdx.y * NQ;
   const int s = blockIdx.z;
   const int kvh = h0 / p.group;
-  const int N = p.n_new;
+  // Uniform batches index the prompt tensors as [sequence][token] (rows past N read as zero); ragged batches as one
+  // flat row axis starting at the sequence's first row (rows past N belong to the next sequence and are masked).
+  const int N = p.cu_seqlens ? p.cu_seqlens[s + 1] - p.cu_seqlens[s] : p.n_new;
+  const int row0 = p.cu_seqlens ? p.cu_seqlens[s] : 0;
+  const int tma_seq = p.cu_seqlens ? 0 : s;
+  const size_t out_row0 = p.cu_seqlens ? (size_t)row0 : (size_t)s * N;
+  if (t0 >= N) return;  // ragged: the grid is sized for the longest sequence (nothing is allocated yet)
   int H = p.hist_lens[s];
   if (H < 0 || p.num_pages <= 0) H = 0;
   {
@@ -410,7 +417,7 @@ __global__ void __launch_bounds__(64 + 128 * NQ, 1)
       mbar_arrive_expect_tx(q_full, NQ * kTileBytes);
       for (int q = 0; q < NQ; ++q)
         for (int kb = 0; kb < 2; ++kb)
-          tma_load_4d(sQ + q * kTileBytes + kb * kHalfTileBytes, &tm_q, kb * 64, h0 + q, t0, s, q_full);
+          tma_load_4d(sQ + q * kTileBytes + kb * kHalfTileBytes, &tm_q, kb * 64, h0 + q, row0 + t0, tma_seq, q_full);
       PAL_MARK(p, 1, 1u);
     }
     for (int j = 0; j < num_tiles && ok; ++j) {
@@ -443,7 +450,7 @@ __global__ void __launch_bounds__(64 + 128 * NQ, 1)
         const int jd = j - hist_tiles;
         mbar_arrive_expect_tx(&k_full[st], kTileBytes);
         for (int kb = 0; kb < 2; ++kb)
-          tma_load_4d(sK + st * kTileBytes + kb * kHalfTileBytes, &tm_k, kb * 64, kvh, jd * kTile, s, &k_full[st]);
+          tma_load_4d(sK + st * kTileBytes + kb * kHalfTileBytes, &tm_k, kb * 64, kvh, row0 + jd * kTile, tma_seq, &k_full[st]);
         PAL_MARK(p, 2, 1u + j);
       }
       // ---- V ----
@@ -461,7 +468,7 @@ __global__ void __launch_bounds__(64 + 128 * NQ, 1)
         const int jd = j - hist_tiles;
         mbar_arrive_expect_tx(&v_full[st], kTileBytes);
         for (int nb = 0; nb < 2; ++nb)
-          tma_load_4d(sV + st * kTileBytes + nb * kHalfTileBytes, &tm_v, nb * 64, kvh, jd * kTile, s, &v_full[st]);
+          tma_load_4d(sV + st * kTileBytes + nb * kHalfTileBytes, &tm_v, nb * 64, kvh, row0 + jd * kTile, tma_seq, &v_full[st]);
         PAL_MARK(p, 3, 1u + j);
       }
     }
@@ -669,7 +676,7 @@ __global__ void __launch_bounds__(64 + 128 * NQ, 1)
     if (ok) {
       tc_fence_after();
       const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
-      T* orow = static_cast<T*>(p.out) + (((size_t)s * N + qi) * p.num_q_heads + h0 + q) * kD;
+      T* orow = static_cast<T*>(p.out) + ((out_row0 + qi) * p.num_q_heads + h0 + q) * kD;
 #pragma unroll
       for (int c4 = 0; c4 < 4; ++c4) {
         uint32_t v[32];
@@ -768,6 +775,7 @@ int launch_prefill_tcgen05(const PrefillArgs& a, cudaStream_t stream) {
   p.k_pool = a.k_pool;
   p.page_table = a.page_table;
   p.hist_lens = a.history_lens;
+  p.cu_seqlens = a.cu_seqlens;
   p.out = a.out;
   p.status = &static_cast<WorkspaceHeader*>(a.workspace)->status;
   p.trace = nullptr;
@@ -783,7 +791,9 @@ int launch_prefill_tcgen05(const PrefillArgs& a, cudaStream_t stream) {
   p.num_pages = a.num_pages;
   p.scale_log2 = a.scale * kLog2e;
 
-  const cuuint64_t S = a.num_seqs, N = a.tokens_per_seq, Hq = a.num_q_heads, Hkv = a.num_kv_heads;
+  // ragged batches: one flat row axis of total_tokens rows (the kernel adds each sequence's first row)
+  const cuuint64_t S = a.cu_seqlens ? 1 : a.num_seqs, N = a.cu_seqlens ? (cuuint64_t)a.total_tokens : a.tokens_per_seq;
+  const cuuint64_t Hq = a.num_q_heads, Hkv = a.num_kv_heads;
   CUtensorMap mq, mk, mv, mvp;
   {
     const cuuint64_t dims[4] = {kD, Hq, N, S};

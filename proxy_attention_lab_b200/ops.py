@@ -377,6 +377,62 @@ def paged_attention_prefill(q_prompt, k_prompt, v_prompt, k_cache_paged, v_cache
     return out
 
 
+def paged_attention_prefill_ragged(q_prompt, k_prompt, v_prompt, k_cache_paged, v_cache_paged, page_table, context_len_arr,
+                                   cu_seqlens, *, max_new_tokens=None, stream=None, impl="auto", scale=None):
+    """``paged_attention_prefill`` for batches whose sequences bring different numbers of new tokens.
+
+    ``cu_seqlens [S + 1]`` (int32, starting at 0) gives each sequence's first row in ``q_prompt [T, Hq, D]`` and
+    ``k_prompt / v_prompt [T, Hkv, D]``; sequence ``s`` owns rows ``cu_seqlens[s] .. cu_seqlens[s+1] - 1``.  A count of 1
+    is a decode step, so prefill chunks and decode steps can share one call.  ``max_new_tokens`` (the largest count)
+    is read back from ``cu_seqlens`` when not given, which synchronises with the device.  Returns ``[T*Hq, D]``.
+    """
+    for name, t in (("q_prompt", q_prompt), ("k_prompt", k_prompt), ("v_prompt", v_prompt),
+                    ("k_cache_paged", k_cache_paged), ("v_cache_paged", v_cache_paged), ("page_table", page_table),
+                    ("context_len_arr", context_len_arr), ("cu_seqlens", cu_seqlens)):
+        _need_cuda(name, t)
+    if v_cache_paged.dim() != 4 or k_cache_paged.dim() != 5:
+        raise ValueError("k_cache_paged must be 5-D and v_cache_paged 4-D")
+    num_pages, hkv, d, tpp = v_cache_paged.shape
+    if q_prompt.dim() != 3 or k_prompt.dim() != 3 or v_prompt.dim() != 3:
+        raise ValueError("q_prompt, k_prompt and v_prompt must be 3-D [tokens, heads, head_dim]")
+    if not (q_prompt.dtype == k_prompt.dtype == v_prompt.dtype == k_cache_paged.dtype == v_cache_paged.dtype):
+        raise ValueError("all data tensors must share one dtype")
+    total, hq, dq = q_prompt.shape
+    if dq != d or tuple(k_prompt.shape) != (total, hkv, d) or tuple(v_prompt.shape) != (total, hkv, d):
+        raise ValueError("prompt tensor shapes do not match the cache (expected k/v [tokens, kv_heads, head_dim])")
+    if page_table.dim() != 2:
+        raise ValueError("page_table must be 2-D [num_sequences, max_logical_pages]")
+    S = context_len_arr.numel()
+    if cu_seqlens.dim() != 1 or cu_seqlens.numel() != S + 1:
+        raise ValueError("cu_seqlens must hold num_sequences + 1 row offsets")
+    if page_table.shape[0] < S:
+        raise ValueError("page_table has fewer rows than there are sequences")
+    if hq % hkv != 0:
+        raise ValueError(f"num_q_heads ({hq}) must be a multiple of num_kv_heads ({hkv})")
+    dev = q_prompt.device
+    out = torch.empty((total * hq, d), dtype=q_prompt.dtype, device=dev)
+    if total == 0 or S == 0:
+        return out
+    cu = _index32("cu_seqlens", cu_seqlens)
+    if max_new_tokens is None:
+        max_new_tokens = int((cu[1:] - cu[:-1]).max().item())
+    q, k, v = _contig(q_prompt), _contig(k_prompt), _contig(v_prompt)
+    if not (k_cache_paged.is_contiguous() and v_cache_paged.is_contiguous()):
+        raise ValueError("the page pools must be contiguous")
+    pt = _index32("page_table", page_table)
+    ctx = _index32("context_len_arr", context_len_arr)
+    with torch.cuda.device(dev):
+        ws = _workspace(lib.pal_prefill_workspace_bytes(S, int(max_new_tokens), hq, hkv, d), dev)
+        rc = lib.pal_paged_attention_prefill_ragged(q.data_ptr(), k.data_ptr(), v.data_ptr(), _ptr(k_cache_paged),
+                                                    _ptr(v_cache_paged), _ptr(pt), ctx.data_ptr(), cu.data_ptr(), out.data_ptr(),
+                                                    S, total, int(max_new_tokens), hq, hkv, d, tpp, num_pages, pt.shape[1],
+                                                    0.0 if scale is None else float(scale), _dtype_code(q.dtype),
+                                                    PREFILL_IMPL[impl] if isinstance(impl, str) else int(impl), ws.data_ptr(),
+                                                    ws.numel(), _stream_ptr(stream, dev))
+        _lib.check(rc)
+    return out
+
+
 def paged_attention(queries, k_cache_pool, v_cache_pool, page_table, sequence_lengths, *, k_prompt=None, v_prompt=None,
                     stream=None, **kw):
     """Single entry point: decode when no prompt K/V are given, prefill otherwise."""

@@ -1,0 +1,92 @@
+"""GPU parity of paged_attention_prefill_ragged (different numbers of new tokens per sequence) against the CPU oracle."""
+
+import pytest
+import torch
+
+from cases import make_decode_case
+from oracle import prefill_ragged_oracle
+
+pytestmark = pytest.mark.gpu
+
+TOL = 2e-3
+IMPLS = ["mma", "tcgen05"]
+
+
+def make_ragged_case(seed, hist_lens, new_counts, hq, hkv, d, tpp=16, dtype=torch.bfloat16, poison_unused=False):
+    base = make_decode_case(seed, hist_lens, hq, hkv, d, tpp=tpp, dtype=dtype, poison_unused=poison_unused)
+    g = torch.Generator().manual_seed(seed + 2000)
+    total = sum(new_counts)
+    q = torch.randn((total, hq, d), generator=g).to(dtype)
+    k = torch.randn((total, hkv, d), generator=g).to(dtype)
+    v = torch.randn((total, hkv, d), generator=g).to(dtype)
+    cu = torch.tensor([0] + torch.tensor(new_counts).cumsum(0).tolist(), dtype=torch.int32)
+    return dict(q=q, k=k, v=v, k_pool=base.k_pool, v_pool=base.v_pool, table=base.page_table,
+                hist=torch.tensor(hist_lens, dtype=torch.int32), cu=cu)
+
+
+def run(pal, cuda, c, **kw):
+    out = pal.paged_attention_prefill_ragged(c["q"].to(cuda), c["k"].to(cuda), c["v"].to(cuda), c["k_pool"].to(cuda),
+                                             c["v_pool"].to(cuda), c["table"].to(cuda), c["hist"].to(cuda), c["cu"].to(cuda), **kw)
+    torch.cuda.synchronize()
+    return out.cpu()
+
+
+def check(pal, cuda, c, impl):
+    ref = prefill_ragged_oracle(c["q"], c["k"], c["v"], c["k_pool"], c["v_pool"], c["table"], c["hist"], c["cu"])
+    out = run(pal, cuda, c, impl=impl)
+    assert out.shape == ref.shape and out.dtype == c["q"].dtype
+    assert torch.isfinite(out.float()).all()
+    diff = (out.float() - ref).abs()
+    ulp = torch.maximum(ref.abs(), torch.tensor(1e-3)) * (2.0 ** -7 if out.dtype == torch.bfloat16 else 2.0 ** -10)
+    bad = (diff > TOL) & (diff > ulp)
+    assert not bad.any(), f"max-abs {diff.max().item()} with {int(bad.sum())} elements out of tolerance"
+
+
+@pytest.mark.parametrize("impl", IMPLS)
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+def test_mixed_counts_around_tile_edges(pal, cuda, impl, dtype):
+    """Counts on both sides of the 64- and 128-row tiles, single tokens (decode steps) and an empty sequence in one batch."""
+    counts = [1, 300, 0, 64, 127, 128, 129, 5, 1, 200]
+    hist = [100, 0, 50, 129, 16, 0, 1000, 77, 2048, 255]
+    check(pal, cuda, make_ragged_case(11, hist, counts, 8, 2, 128, dtype=dtype), impl)
+
+
+@pytest.mark.parametrize("impl", IMPLS)
+def test_poisoned_unused_slots_and_foreign_rows(pal, cuda, impl):
+    """Unused page slots hold NaN; a tile of a short sequence also covers rows of its neighbours, which must stay masked."""
+    counts = [3, 130, 2, 61]
+    hist = [5, 200, 0, 33]
+    check(pal, cuda, make_ragged_case(12, hist, counts, 4, 2, 128, poison_unused=True), impl)
+
+
+@pytest.mark.parametrize("d,tpp", [(64, 16), (80, 16), (96, 32), (256, 16), (32, 32)])
+def test_other_shapes_mma(pal, cuda, d, tpp):
+    counts = [70, 1, 33, 128]
+    hist = [40, 300, 0, 65]
+    check(pal, cuda, make_ragged_case(13, hist, counts, 6, 3, d, tpp=tpp), "mma")
+
+
+@pytest.mark.parametrize("impl", IMPLS)
+def test_equal_counts_match_the_uniform_call_bit_for_bit(pal, cuda, impl):
+    counts = [192] * 3
+    c = make_ragged_case(14, [0, 500, 129], counts, 8, 4, 128)
+    ragged = run(pal, cuda, c, impl=impl)
+    uniform = pal.paged_attention_prefill(c["q"].to(cuda), c["k"].to(cuda), c["v"].to(cuda), c["k_pool"].to(cuda),
+                                          c["v_pool"].to(cuda), c["table"].to(cuda), c["hist"].to(cuda), impl=impl).cpu()
+    assert torch.equal(ragged.view(torch.int16), uniform.view(torch.int16))
+
+
+def test_auto_choice_and_explicit_maximum(pal, cuda):
+    counts = [256, 17, 1]
+    c = make_ragged_case(15, [64, 0, 700], counts, 32, 8, 128)
+    ref = prefill_ragged_oracle(c["q"], c["k"], c["v"], c["k_pool"], c["v_pool"], c["table"], c["hist"], c["cu"])
+    for kw in (dict(), dict(max_new_tokens=256), dict(max_new_tokens=300)):
+        out = run(pal, cuda, c, **kw)
+        diff = (out.float() - ref).abs()
+        ulp = torch.maximum(ref.abs(), torch.tensor(1e-3)) * 2.0 ** -7
+        assert not ((diff > TOL) & (diff > ulp)).any()
+
+
+def test_empty_batch(pal, cuda):
+    c = make_ragged_case(16, [10, 20], [0, 0], 4, 2, 128)
+    assert run(pal, cuda, c).shape == (0, 128)
