@@ -249,7 +249,9 @@ int launch_fill(const FillArgs& a, cudaStream_t stream) {
   int parts = 1;
   while (parts < 8 && vec_per_token % (parts * 2) == 0 && vec_per_token / parts > 64) parts *= 2;
   const size_t grouped_smem = 2 * (size_t)kGroupTokens * ((size_t)(vec_per_token / parts) * 16 + 16);
-  if (a.num_tokens >= kGroupTokens && a.tokens_per_page % 8 == 0 && grouped_smem <= 160 * 1024) {
+  // Below a few hundred tokens (a decode step appends one token per sequence) the call is latency-bound and the
+  // scattered kernel, with its single dependent load per thread, finishes sooner.
+  if (a.num_tokens >= 256 && a.tokens_per_page % 8 == 0 && grouped_smem <= 160 * 1024) {
     long long groups = (a.num_tokens + kGroupTokens - 1) / kGroupTokens * parts;
     const long long max_groups = 148LL * 32;
     if (groups > max_groups) groups = max_groups;

@@ -104,18 +104,19 @@ def test_scatter_config_reference_triple(pal, cuda):
 def test_runs_mixed_with_scattered_and_skipped_tokens(pal, cuda, dtype, hkv, d, tpp):
     """Token lists that mix appended runs (aligned and not), isolated tokens and slots that must be skipped, with a
     length that is not a multiple of the kernel's token group: both store paths and their edges, bit for bit."""
-    P = 96
+    P = 512
     g = torch.Generator().manual_seed(hkv * 1000 + d + tpp)
     pages = torch.randperm(P, generator=g).tolist()
     slots = []
-    for start, n in ((0, 40), (5, 23), (tpp - 1, 3), (3, 1), (8 % tpp, 8), (0, tpp), (1, 2 * tpp + 7)):
-        pgs = [pages.pop() for _ in range((start + n) // tpp + 1)]
-        slots += [pgs[(start + i) // tpp] * tpp + (start + i) % tpp for i in range(n)]
-        slots += [-1, P * tpp + 3]  # skipped entries between the runs
-        slots += [pages.pop() * tpp + int(torch.randint(0, tpp, (1,), generator=g))]  # an isolated token
+    for rep in range(4):  # enough tokens for the grouped kernel to be the one that runs
+        for start, n in ((0, 40), (5, 23), (tpp - 1, 3), (3, 1), (8 % tpp, 8), (0, tpp), (1, 2 * tpp + 7 + rep)):
+            pgs = [pages.pop() for _ in range((start + n) // tpp + 1)]
+            slots += [pgs[(start + i) // tpp] * tpp + (start + i) % tpp for i in range(n)]
+            slots += [-1, P * tpp + 3]  # skipped entries between the runs
+            slots += [pages.pop() * tpp + int(torch.randint(0, tpp, (1,), generator=g))]  # an isolated token
     slots = torch.tensor(slots, dtype=torch.int64)
     T = slots.numel()
-    assert T % 16 != 0
+    assert T >= 256 and T % 16 != 0
     keys = torch.randn((T, hkv, d), generator=g).to(dtype)
     vals = torch.randn((T, hkv, d), generator=g).to(dtype)
     k, v = _pools(P, hkv, d, tpp, dtype, sentinel=0x3C3C)
