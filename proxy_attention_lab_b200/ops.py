@@ -10,6 +10,7 @@ no fallback path.
 
 from __future__ import annotations
 
+import functools
 import math
 
 import torch
@@ -61,8 +62,40 @@ def _ptr(t) -> int:
     return 0 if t is None or t.numel() == 0 else t.data_ptr()
 
 
-def _workspace(nbytes: int, device) -> torch.Tensor:
-    return torch.empty(max(int(nbytes), 256), dtype=torch.uint8, device=device)
+_WORKSPACES: dict = {}
+
+
+def _workspace(nbytes: int, device, stream_ptr: int) -> torch.Tensor:
+    """Scratch for one call.  Calls on one stream run in order, so they share one buffer per (device, stream);
+    it only ever grows, which also keeps its address stable for a caller that captures the call in a CUDA graph."""
+    need = max(int(nbytes), 256)
+    key = (device.index, stream_ptr)
+    ws = _WORKSPACES.get(key)
+    if ws is None or ws.numel() < need:
+        ws = torch.empty(max(need, 4096), dtype=torch.uint8, device=device)
+        _WORKSPACES[key] = ws
+    return ws
+
+
+class _NoGuard:
+    def __enter__(self):
+        return None
+
+    def __exit__(self, *exc):
+        return False
+
+
+_NO_GUARD = _NoGuard()
+
+
+def _on(device):
+    """Device guard that costs nothing when `device` is already current."""
+    return _NO_GUARD if torch.cuda.current_device() == device.index else torch.cuda.device(device)
+
+
+@functools.lru_cache(maxsize=256)
+def _decode_ws_bytes(S, hq, hkv, d, tpp, mp, pp) -> int:
+    return lib.pal_decode_workspace_bytes(S, hq, hkv, d, tpp, mp, pp)
 
 
 # ---------------------------------------------------------------------------------------------
@@ -145,7 +178,7 @@ def fill_kv_pages(
         return global_key_pool, global_value_pool
     new_keys, new_values = _contig(new_keys), _contig(new_values)
     dev = global_value_pool.device
-    with torch.cuda.device(dev):
+    with _on(dev):
         sp = _stream_ptr(stream, dev)
         if slot_mapping is not None:
             _need_cuda("slot_mapping", slot_mapping)
@@ -223,13 +256,13 @@ def paged_attention_decode(queries, k_cache_pool, v_cache_pool, page_table, sequ
     pt = _index32("page_table", page_table)
     lens = _index32("sequence_lengths", sequence_lengths)
     pp = _lib.PAL_DECODE_AUTO if partition_pages is None else int(partition_pages)
-    with torch.cuda.device(dev):
-        nbytes = lib.pal_decode_workspace_bytes(S, hq, hkv, d, tpp, pt.shape[1], pp)
-        ws = _workspace(nbytes, dev)
+    with _on(dev):
+        sp = _stream_ptr(stream, dev)
+        ws = _workspace(_decode_ws_bytes(S, hq, hkv, d, tpp, pt.shape[1], pp), dev, sp)
         rc = lib.pal_paged_attention_decode(q.data_ptr(), _ptr(k_cache_pool), _ptr(v_cache_pool), _ptr(pt), lens.data_ptr(),
                                             out.data_ptr(), S, hq, hkv, d, tpp, num_pages, pt.shape[1],
                                             0.0 if scale is None else float(scale), _dtype_code(q.dtype), pp,
-                                            ws.data_ptr(), ws.numel(), _stream_ptr(stream, dev))
+                                            ws.data_ptr(), ws.numel(), sp)
         _lib.check(rc)
     return out
 
@@ -256,13 +289,13 @@ def paged_attention_decode_append(new_keys, new_values, queries, k_cache_pool, v
     pt = _index32("page_table", page_table)
     lens = _index32("sequence_lengths", sequence_lengths)
     pp = _lib.PAL_DECODE_AUTO if partition_pages is None else int(partition_pages)
-    with torch.cuda.device(dev):
-        nbytes = lib.pal_decode_workspace_bytes(S, hq, hkv, d, tpp, pt.shape[1], pp)
-        ws = _workspace(nbytes, dev)
+    with _on(dev):
+        sp = _stream_ptr(stream, dev)
+        ws = _workspace(_decode_ws_bytes(S, hq, hkv, d, tpp, pt.shape[1], pp), dev, sp)
         rc = lib.pal_paged_attention_decode_append(nk.data_ptr(), nv.data_ptr(), q.data_ptr(), _ptr(k_cache_pool),
                                                    _ptr(v_cache_pool), _ptr(pt), lens.data_ptr(), out.data_ptr(), S, hq, hkv, d,
                                                    tpp, num_pages, pt.shape[1], 0.0 if scale is None else float(scale),
-                                                   _dtype_code(q.dtype), pp, ws.data_ptr(), ws.numel(), _stream_ptr(stream, dev))
+                                                   _dtype_code(q.dtype), pp, ws.data_ptr(), ws.numel(), sp)
         _lib.check(rc)
     return out
 
@@ -284,14 +317,14 @@ def paged_attention_decode_partials(queries, k_cache_pool, v_cache_pool, page_ta
     q = _contig(queries)
     pt = _index32("page_table", page_table)
     lens = _index32("sequence_lengths", sequence_lengths)
-    with torch.cuda.device(dev):
-        nbytes = lib.pal_decode_workspace_bytes(S, hq, hkv, d, tpp, pt.shape[1], int(partition_pages))
-        ws = _workspace(nbytes, dev)
+    with _on(dev):
+        sp = _stream_ptr(stream, dev)
+        ws = _workspace(_decode_ws_bytes(S, hq, hkv, d, tpp, pt.shape[1], int(partition_pages)), dev, sp)
         rc = lib.pal_paged_attention_decode_partials(q.data_ptr(), _ptr(k_cache_pool), _ptr(v_cache_pool), _ptr(pt),
                                                      lens.data_ptr(), m.data_ptr(), l.data_ptr(), acc.data_ptr(), S, hq, hkv, d,
                                                      tpp, num_pages, pt.shape[1], 0.0 if scale is None else float(scale),
                                                      _dtype_code(q.dtype), int(partition_pages), ws.data_ptr(), ws.numel(),
-                                                     _stream_ptr(stream, dev))
+                                                     sp)
         _lib.check(rc)
     return m, l, acc
 
@@ -366,13 +399,14 @@ def paged_attention_prefill(q_prompt, k_prompt, v_prompt, k_cache_paged, v_cache
         raise ValueError("the page pools must be contiguous")
     pt = _index32("page_table", page_table)
     ctx = _index32("context_len_arr", context_len_arr)
-    with torch.cuda.device(dev):
-        ws = _workspace(lib.pal_prefill_workspace_bytes(S, n, hq, hkv, d), dev)
+    with _on(dev):
+        sp = _stream_ptr(stream, dev)
+        ws = _workspace(lib.pal_prefill_workspace_bytes(S, n, hq, hkv, d), dev, sp)
         rc = lib.pal_paged_attention_prefill(q.data_ptr(), k.data_ptr(), v.data_ptr(), _ptr(k_cache_paged), _ptr(v_cache_paged),
                                              _ptr(pt), ctx.data_ptr(), out.data_ptr(), S, n, hq, hkv, d, tpp, num_pages,
                                              pt.shape[1], 0.0 if scale is None else float(scale), _dtype_code(q.dtype),
                                              PREFILL_IMPL[impl] if isinstance(impl, str) else int(impl), ws.data_ptr(),
-                                             ws.numel(), _stream_ptr(stream, dev))
+                                             ws.numel(), sp)
         _lib.check(rc)
     return out
 
@@ -421,14 +455,15 @@ def paged_attention_prefill_ragged(q_prompt, k_prompt, v_prompt, k_cache_paged, 
         raise ValueError("the page pools must be contiguous")
     pt = _index32("page_table", page_table)
     ctx = _index32("context_len_arr", context_len_arr)
-    with torch.cuda.device(dev):
-        ws = _workspace(lib.pal_prefill_workspace_bytes(S, int(max_new_tokens), hq, hkv, d), dev)
+    with _on(dev):
+        sp = _stream_ptr(stream, dev)
+        ws = _workspace(lib.pal_prefill_workspace_bytes(S, int(max_new_tokens), hq, hkv, d), dev, sp)
         rc = lib.pal_paged_attention_prefill_ragged(q.data_ptr(), k.data_ptr(), v.data_ptr(), _ptr(k_cache_paged),
                                                     _ptr(v_cache_paged), _ptr(pt), ctx.data_ptr(), cu.data_ptr(), out.data_ptr(),
                                                     S, total, int(max_new_tokens), hq, hkv, d, tpp, num_pages, pt.shape[1],
                                                     0.0 if scale is None else float(scale), _dtype_code(q.dtype),
                                                     PREFILL_IMPL[impl] if isinstance(impl, str) else int(impl), ws.data_ptr(),
-                                                    ws.numel(), _stream_ptr(stream, dev))
+                                                    ws.numel(), sp)
         _lib.check(rc)
     return out
 
