@@ -149,7 +149,8 @@ def build_decode(cfg, device, seed, hkv_local=None):
     tpp, d, hq = cfg["tpp"], cfg["d"], cfg["hq"]
     hkv = hkv_local or cfg["hkv"]
     hq_local = hq * hkv // cfg["hkv"]
-    lens = make_lengths(seed, cfg["S"], cfg["lo"], cfg["hi"])
+    # The same context lengths on every rank (weak scaling = the same work per GPU as N grows); pages and data differ.
+    lens = make_lengths(0, cfg["S"], cfg["lo"], cfg["hi"])
     npg = (lens + tpp - 1) // tpp
     P, MP = int(npg.sum()), int(npg.max())
     g = torch.Generator().manual_seed(seed + 1)
