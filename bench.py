@@ -318,6 +318,8 @@ class HostPipeline:
         self.s_in, self.s_out = torch.cuda.Stream(device), torch.cuda.Stream(device)
         self.ready = [torch.cuda.Event() for _ in range(2)]  # the inputs of slot b are on the device
         self.free = [torch.cuda.Event() for _ in range(2)]   # the kernels that read slot b have finished
+        self.copied = [torch.cuda.Event() for _ in range(2)]  # the result of slot b has reached the host
+        self.keep = [None, None]
         self.i = 0
         for e in self.free:
             e.record()
@@ -335,10 +337,15 @@ class HostPipeline:
         out = self.call(self.bufs[b])
         self.free[b].record(cur)
         if self.out_host is not None:
+            # the result tensor is kept alive until its copy has finished (two steps later it surely has), so the
+            # caching allocator never has to track it across streams
+            if self.keep[b] is not None:
+                self.copied[b].synchronize()
             with torch.cuda.stream(self.s_out):
                 self.s_out.wait_event(self.free[b])
                 self.out_host.copy_(out, non_blocking=True)
-                out.record_stream(self.s_out)
+                self.copied[b].record(self.s_out)
+            self.keep[b] = out
 
     def drain(self):
         cur = torch.cuda.current_stream()
