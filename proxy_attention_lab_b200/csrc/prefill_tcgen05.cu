@@ -15,7 +15,9 @@
 //   warp 1        issues every tcgen05.mma and tcgen05.commit: the warp stays converged and the thread picked by
 //                 elect.sync issues, which lets the compiler keep descriptors in uniform registers (a branch
 //                 on lane 0 instead costs several hundred cycles of the issuing thread per key tile).
-//   warps 2..     one softmax warpgroup (128 threads = 128 rows = 128 TMEM lanes) per query head.
+//   warps 2..     one softmax warpgroup (128 threads = 128 rows = 128 TMEM lanes) per query head; at the end it
+//                 scales O by 1/l, stages the tile in the head's (by then unused) Q buffer and writes it out with
+//                 two TMA stores.
 //
 // Shared-memory operand layouts and their UMMA descriptors
 //   Q, dense K   [2 k-blocks][128 rows][64 el]  K-major, SWIZZLE_128B, SBO 1024; +32 B per K=16 step
@@ -106,6 +108,16 @@ __device__ __forceinline__ bool elect_one() {
   uint32_t pred;
   asm volatile("{\n\t.reg .pred p;\n\telect.sync _|p, 0xffffffff;\n\tselp.b32 %0, 1, 0, p;\n\t}" : "=r"(pred));
   return pred != 0;
+}
+__device__ __forceinline__ void tma_store_4d(const CUtensorMap* map, const void* src, int c0, int c1, int c2, int c3) {
+  asm volatile("cp.async.bulk.tensor.4d.global.shared::cta.bulk_group [%0, {%2, %3, %4, %5}], [%1];" ::"l"(
+                   reinterpret_cast<uint64_t>(map)),
+               "r"(smem_u32(src)), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+               : "memory");
+}
+__device__ __forceinline__ void tma_store_commit_and_wait_read() {
+  asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+  asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
 }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
@@ -335,7 +347,8 @@ struct TcSmem {
 template <typename T, int NQ>
 __global__ void __launch_bounds__(64 + 128 * NQ, 1)
     prefill_tcgen05_kernel(const TcParams p, const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
-                           const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_vpool) {
+                           const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_vpool,
+                           const __grid_constant__ CUtensorMap tm_out) {
   extern __shared__ unsigned char smem_raw[];
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   using SM = TcSmem<NQ>;
@@ -673,25 +686,46 @@ __global__ void __launch_bounds__(64 + 128 * NQ, 1)
     // ---- epilogue: O / l -> out[((s*N + qi)*Hq + h0 + q)*D + d] ----
     if (ok) ok = mbar_wait(&o_done[q], (num_tiles - 1) & 1, p.status);
     if (tid == 64) PAL_MARK(p, 14, 1u + ok);
+    // Full tiles (and partial ones of uniform batches, which the tensor map clips at the sequence's end) leave through
+    // shared memory: the head's Q tile is no longer read by any MMA, has exactly the size and swizzled layout of the
+    // output tile, and two TMA stores write it out in whole lines.  A partial tile of a ragged batch would run into the
+    // next sequence's rows, so it is stored row by row from registers.
+    const bool tma_out = p.cu_seqlens == nullptr || t0 + kTile <= N;
     if (ok) {
       tc_fence_after();
       const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
       T* orow = static_cast<T*>(p.out) + ((out_row0 + qi) * p.num_q_heads + h0 + q) * kD;
+      unsigned char* stage = sQ + q * kTileBytes + row * 128;
 #pragma unroll
       for (int c4 = 0; c4 < 4; ++c4) {
         uint32_t v[32];
         tmem_ld32(tO + c4 * 32, v);
         tmem_wait_ld();
-        if (qi < N) {
 #pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            uint4 w;
-            w.x = Mma16816<T>::pack(__uint_as_float(v[8 * i + 0]) * inv, __uint_as_float(v[8 * i + 1]) * inv);
-            w.y = Mma16816<T>::pack(__uint_as_float(v[8 * i + 2]) * inv, __uint_as_float(v[8 * i + 3]) * inv);
-            w.z = Mma16816<T>::pack(__uint_as_float(v[8 * i + 4]) * inv, __uint_as_float(v[8 * i + 5]) * inv);
-            w.w = Mma16816<T>::pack(__uint_as_float(v[8 * i + 6]) * inv, __uint_as_float(v[8 * i + 7]) * inv);
+        for (int i = 0; i < 4; ++i) {
+          uint4 w;
+          w.x = Mma16816<T>::pack(__uint_as_float(v[8 * i + 0]) * inv, __uint_as_float(v[8 * i + 1]) * inv);
+          w.y = Mma16816<T>::pack(__uint_as_float(v[8 * i + 2]) * inv, __uint_as_float(v[8 * i + 3]) * inv);
+          w.z = Mma16816<T>::pack(__uint_as_float(v[8 * i + 4]) * inv, __uint_as_float(v[8 * i + 5]) * inv);
+          w.w = Mma16816<T>::pack(__uint_as_float(v[8 * i + 6]) * inv, __uint_as_float(v[8 * i + 7]) * inv);
+          if (tma_out) {
+            // 16-byte chunk j = 4 c4 + i of the row: 64-element block j / 8, chunk j % 8 xor-swizzled with the row
+            const int j = 4 * c4 + i;
+            *reinterpret_cast<uint4*>(stage + (j >> 3) * kHalfTileBytes + (((j & 7) ^ (row & 7)) << 4)) = w;
+          } else if (qi < N) {
             *reinterpret_cast<uint4*>(orow + c4 * 32 + i * 8) = w;
           }
+        }
+      }
+      if (tma_out) {
+        fence_proxy_async_smem();
+        __syncwarp();
+        // p_full[q] has seen num_tiles phases; one more collects the head's four warps
+        if (lane == 0) mbar_arrive(&p_full[q]);
+        if (lane_group == 0 && lane == 0 && mbar_wait(&p_full[q], num_tiles & 1, p.status)) {
+          for (int kb = 0; kb < 2; ++kb)
+            tma_store_4d(&tm_out, sQ + q * kTileBytes + kb * kHalfTileBytes, kb * 64, h0 + q, row0 + t0, tma_seq);
+          tma_store_commit_and_wait_read();
         }
       }
     }
@@ -741,7 +775,7 @@ bool encode_map(CUtensorMap* map, int dtype, int rank, const void* base, const c
 
 template <typename T, int NQ>
 int launch_tc(const TcParams& p, const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv,
-              const CUtensorMap& mvp, cudaStream_t stream) {
+              const CUtensorMap& mvp, const CUtensorMap& mo, cudaStream_t stream) {
   auto kern = prefill_tcgen05_kernel<T, NQ>;
   static bool configured[64] = {};
   int dev = 0;
@@ -752,7 +786,7 @@ int launch_tc(const TcParams& p, const CUtensorMap& mq, const CUtensorMap& mk, c
     configured[dev] = true;
   }
   dim3 grid((p.n_new + kTile - 1) / kTile, p.num_q_heads / NQ, p.num_seqs);
-  kern<<<grid, 64 + 128 * NQ, TcSmem<NQ>::kTotal, stream>>>(p, mq, mk, mv, mvp);
+  kern<<<grid, 64 + 128 * NQ, TcSmem<NQ>::kTotal, stream>>>(p, mq, mk, mv, mvp, mo);
   return (int)cudaGetLastError();
 }
 
@@ -794,12 +828,13 @@ int launch_prefill_tcgen05(const PrefillArgs& a, cudaStream_t stream) {
   // ragged batches: one flat row axis of total_tokens rows (the kernel adds each sequence's first row)
   const cuuint64_t S = a.cu_seqlens ? 1 : a.num_seqs, N = a.cu_seqlens ? (cuuint64_t)a.total_tokens : a.tokens_per_seq;
   const cuuint64_t Hq = a.num_q_heads, Hkv = a.num_kv_heads;
-  CUtensorMap mq, mk, mv, mvp;
+  CUtensorMap mq, mk, mv, mvp, mo;
   {
     const cuuint64_t dims[4] = {kD, Hq, N, S};
     const cuuint64_t strides[3] = {kD * 2, Hq * kD * 2, N * Hq * kD * 2};
     const cuuint32_t box[4] = {64, 1, kTile, 1};
     if (!encode_map(&mq, a.dtype, 4, a.q_prompt, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B)) return -3;
+    if (!encode_map(&mo, a.dtype, 4, a.out, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B)) return -3;  // out has q's layout
   }
   {
     const cuuint64_t dims[4] = {kD, Hkv, N, S};
@@ -820,9 +855,9 @@ int launch_prefill_tcgen05(const PrefillArgs& a, cudaStream_t stream) {
   if (e != cudaSuccess) return (int)e;
   const bool pair = (p.group % 2) == 0;
   if (a.dtype == 0)
-    return pair ? launch_tc<__half, 2>(p, mq, mk, mv, mvp, stream) : launch_tc<__half, 1>(p, mq, mk, mv, mvp, stream);
-  return pair ? launch_tc<__nv_bfloat16, 2>(p, mq, mk, mv, mvp, stream)
-              : launch_tc<__nv_bfloat16, 1>(p, mq, mk, mv, mvp, stream);
+    return pair ? launch_tc<__half, 2>(p, mq, mk, mv, mvp, mo, stream) : launch_tc<__half, 1>(p, mq, mk, mv, mvp, mo, stream);
+  return pair ? launch_tc<__nv_bfloat16, 2>(p, mq, mk, mv, mvp, mo, stream)
+              : launch_tc<__nv_bfloat16, 1>(p, mq, mk, mv, mvp, mo, stream);
 }
 
 }  // namespace pal
