@@ -603,7 +603,9 @@ def main():
     if rank == 0:
         achieved = achieved_of(per_step)
         # DRAM bytes per launch from one `ncu --set full` capture of the same workload (see profiles/)
-        traffic = {"decode_8b": 1.3866e9}.get(args.workload) if world == 1 else None
+        # fill_append: 0.904 x the algorithmic bytes, from the capture of the reduced case (traffic grows with the tokens)
+        traffic = {"decode_8b": 1.3866e9, "decode_8b_append": 1.3889e9,
+                   "fill_append": 0.904 * alg_per_step}.get(args.workload) if world == 1 else None
         line = {
             "metric": metric, "value": value, "unit": unit, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": per_step * 1e3, "higher_is_better": True, "scaling": scaling, "vs_baseline": None,
