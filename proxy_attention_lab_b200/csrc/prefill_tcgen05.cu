@@ -5,8 +5,9 @@
 // paged_attention_prefill.h.metal:28-389), which handles one key per iteration per simdgroup with
 // scalar FMAs, and its launcher (src/pal_core/src/paged_attention_prefill_primitive.cpp:63-167).
 //
-// One CTA owns 128 consecutive new tokens of NQ (1 or 2) query heads that share a kv head; each
-// head's 128 rows are one M = 128 accumulator tile.  Keys arrive in tiles of 128 tokens: first the
+// One CTA owns NQ (1 or 2) accumulator tiles of M = 128 rows that read the same K / V tiles: 128 consecutive new
+// tokens of two query heads that share a kv head, or - when the heads per kv head are odd in number, e.g. one -
+// two consecutive 128-token query tiles of one head.  Keys arrive in tiles of 128 tokens: first the
 // paged history, then the dense prompt keys up to the diagonal tile.
 //
 //   warp 0        producer: Q / dense K / dense V tiles by TMA (128-byte swizzle); history K pages
@@ -344,7 +345,10 @@ struct TcSmem {
   static constexpr int kTotal = kBars + 256 + 1024;  // + alignment slack
 };
 
-template <typename T, int NQ>
+// NQ accumulator tiles per CTA.  PAIR_TILES = false: tile q is query head h0 + q of one 128-token query tile (heads that
+// share a kv head).  PAIR_TILES = true (NQ = 2): both tiles belong to head h0, tile q holds query tile 2 * blockIdx.x' + q;
+// they share every K / V tile, and the earlier one sees its last key tile fully masked.
+template <typename T, int NQ, bool PAIR_TILES>
 __global__ void __launch_bounds__(64 + 128 * NQ, 1)
     prefill_tcgen05_kernel(const TcParams p, const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                            const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_vpool,
@@ -368,9 +372,12 @@ __global__ void __launch_bounds__(64 + 128 * NQ, 1)
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   // heaviest (latest) query tiles first
-  const int qt = (int)gridDim.x - 1 - (int)blockIdx.x;
+  const int qt_cta = (int)gridDim.x - 1 - (int)blockIdx.x;
+  const int qt = PAIR_TILES ? 2 * qt_cta : qt_cta;   // the CTA's first (or only) query tile
   const int t0 = qt * kTile;
-  const int h0 = blockIdx.y * NQ;
+  const int h0 = PAIR_TILES ? blockIdx.y : blockIdx.y * NQ;
+  constexpr int kHeadStep = PAIR_TILES ? 0 : 1;         // head of accumulator tile q = h0 + q * kHeadStep
+  constexpr int kRowStep = PAIR_TILES ? kTile : 0;      // its first query token = t0 + q * kRowStep
   const int s = blockIdx.z;
   const int kvh = h0 / p.group;
   // Uniform batches index the prompt tensors as [sequence][token] (rows past N read as zero); ragged batches as one
@@ -387,7 +394,8 @@ __global__ void __launch_bounds__(64 + 128 * NQ, 1)
     if (H > cap) H = (int)cap;
   }
   const int hist_tiles = (H + kTile - 1) / kTile;
-  const int dense_tiles = qt + 1;
+  // key tiles of the new tokens up to the diagonal of the CTA's last query tile that exists
+  const int dense_tiles = (PAIR_TILES && t0 + kTile < N ? qt + 1 : qt) + 1;
   const int num_tiles = hist_tiles + dense_tiles;
   // bf16 rounds P with a relative error of up to 2^-8; summed over n keys that leaves about
   // 0.002 / sqrt(n / 3) of absolute error per unit of |v|, which only drops below the 2e-3 target
@@ -430,7 +438,7 @@ __global__ void __launch_bounds__(64 + 128 * NQ, 1)
       mbar_arrive_expect_tx(q_full, NQ * kTileBytes);
       for (int q = 0; q < NQ; ++q)
         for (int kb = 0; kb < 2; ++kb)
-          tma_load_4d(sQ + q * kTileBytes + kb * kHalfTileBytes, &tm_q, kb * 64, h0 + q, row0 + t0, tma_seq, q_full);
+          tma_load_4d(sQ + q * kTileBytes + kb * kHalfTileBytes, &tm_q, kb * 64, h0 + q * kHeadStep, row0 + t0 + q * kRowStep, tma_seq, q_full);
       PAL_MARK(p, 1, 1u);
     }
     for (int j = 0; j < num_tiles && ok; ++j) {
@@ -598,7 +606,9 @@ __global__ void __launch_bounds__(64 + 128 * NQ, 1)
     const uint32_t lane_addr = (uint32_t)(lane_group * 32) << 16;
     const uint32_t tS = tmem_base + lane_addr + q * kTile;
     const uint32_t tO = tmem_base + lane_addr + 2 * kTile + q * kTile;
-    const int qi = t0 + row;                    // index of this row's query token in its sequence
+    const int t0q = t0 + q * kRowStep;          // first query token of this accumulator tile
+    const int diag = t0q / kTile;               // its diagonal key tile among the new tokens
+    const int qi = t0q + row;                   // index of this row's query token in its sequence
     float m_used = -INFINITY, l_run = 0.f;
     bool ok = true;
 
@@ -609,7 +619,7 @@ __global__ void __launch_bounds__(64 + 128 * NQ, 1)
       tc_fence_after();
       if (tid == 64) PAL_MARK(p, 8, 1u + j);
       // which columns need masking at all (warp-uniform), and up to which key offset this row sees
-      const bool need_mask = paged ? ((j + 1) * kTile > H) : (jd == dense_tiles - 1 || (jd + 1) * kTile > N);
+      const bool need_mask = paged ? ((j + 1) * kTile > H) : (jd >= diag || (jd + 1) * kTile > N);
       const int rel_limit = paged ? (H - 1 - j * kTile) : (min(qi, N - 1) - jd * kTile);
 
       // ---- pass 1: row maximum of the scaled scores ----
@@ -690,11 +700,11 @@ __global__ void __launch_bounds__(64 + 128 * NQ, 1)
     // shared memory: the head's Q tile is no longer read by any MMA, has exactly the size and swizzled layout of the
     // output tile, and two TMA stores write it out in whole lines.  A partial tile of a ragged batch would run into the
     // next sequence's rows, so it is stored row by row from registers.
-    const bool tma_out = p.cu_seqlens == nullptr || t0 + kTile <= N;
+    const bool tma_out = p.cu_seqlens == nullptr || t0q + kTile <= N;
     if (ok) {
       tc_fence_after();
       const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
-      T* orow = static_cast<T*>(p.out) + ((out_row0 + qi) * p.num_q_heads + h0 + q) * kD;
+      T* orow = static_cast<T*>(p.out) + ((out_row0 + qi) * p.num_q_heads + h0 + q * kHeadStep) * kD;
       unsigned char* stage = sQ + q * kTileBytes + row * 128;
 #pragma unroll
       for (int c4 = 0; c4 < 4; ++c4) {
@@ -722,9 +732,10 @@ __global__ void __launch_bounds__(64 + 128 * NQ, 1)
         __syncwarp();
         // p_full[q] has seen num_tiles phases; one more collects the head's four warps
         if (lane == 0) mbar_arrive(&p_full[q]);
-        if (lane_group == 0 && lane == 0 && mbar_wait(&p_full[q], num_tiles & 1, p.status)) {
+        // (a paired CTA's second query tile may lie entirely past the sequence's end: nothing to write then)
+        if (lane_group == 0 && lane == 0 && mbar_wait(&p_full[q], num_tiles & 1, p.status) && t0q < N) {
           for (int kb = 0; kb < 2; ++kb)
-            tma_store_4d(&tm_out, sQ + q * kTileBytes + kb * kHalfTileBytes, kb * 64, h0 + q, row0 + t0, tma_seq);
+            tma_store_4d(&tm_out, sQ + q * kTileBytes + kb * kHalfTileBytes, kb * 64, h0 + q * kHeadStep, row0 + t0q, tma_seq);
           tma_store_commit_and_wait_read();
         }
       }
@@ -773,10 +784,10 @@ bool encode_map(CUtensorMap* map, int dtype, int rank, const void* base, const c
   return true;
 }
 
-template <typename T, int NQ>
+template <typename T, int NQ, bool PAIR_TILES>
 int launch_tc(const TcParams& p, const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv,
               const CUtensorMap& mvp, const CUtensorMap& mo, cudaStream_t stream) {
-  auto kern = prefill_tcgen05_kernel<T, NQ>;
+  auto kern = prefill_tcgen05_kernel<T, NQ, PAIR_TILES>;
   static bool configured[64] = {};
   int dev = 0;
   cudaGetDevice(&dev);
@@ -785,7 +796,8 @@ int launch_tc(const TcParams& p, const CUtensorMap& mq, const CUtensorMap& mk, c
     if (e != cudaSuccess) return (int)e;
     configured[dev] = true;
   }
-  dim3 grid((p.n_new + kTile - 1) / kTile, p.num_q_heads / NQ, p.num_seqs);
+  const int num_qt = (p.n_new + kTile - 1) / kTile;
+  dim3 grid(PAIR_TILES ? (num_qt + 1) / 2 : num_qt, PAIR_TILES ? p.num_q_heads : p.num_q_heads / NQ, p.num_seqs);
   kern<<<grid, 64 + 128 * NQ, TcSmem<NQ>::kTotal, stream>>>(p, mq, mk, mv, mvp, mo);
   return (int)cudaGetLastError();
 }
@@ -853,11 +865,18 @@ int launch_prefill_tcgen05(const PrefillArgs& a, cudaStream_t stream) {
   }
   cudaError_t e = cudaMemsetAsync(a.workspace, 0, 8, stream);
   if (e != cudaSuccess) return (int)e;
-  const bool pair = (p.group % 2) == 0;
-  if (a.dtype == 0)
-    return pair ? launch_tc<__half, 2>(p, mq, mk, mv, mvp, mo, stream) : launch_tc<__half, 1>(p, mq, mk, mv, mvp, mo, stream);
-  return pair ? launch_tc<__nv_bfloat16, 2>(p, mq, mk, mv, mvp, mo, stream)
-              : launch_tc<__nv_bfloat16, 1>(p, mq, mk, mv, mvp, mo, stream);
+  // Heads that share a kv head go two to a CTA; otherwise (odd group sizes, e.g. one query head per kv head) two query
+  // tiles of one head do, and only a sequence of a single query tile leaves a CTA with one accumulator tile.
+  const bool pair_heads = (p.group % 2) == 0;
+  const bool pair_tiles = !pair_heads && a.tokens_per_seq > kTile;
+  if (a.dtype == 0) {
+    if (pair_heads) return launch_tc<__half, 2, false>(p, mq, mk, mv, mvp, mo, stream);
+    if (pair_tiles) return launch_tc<__half, 2, true>(p, mq, mk, mv, mvp, mo, stream);
+    return launch_tc<__half, 1, false>(p, mq, mk, mv, mvp, mo, stream);
+  }
+  if (pair_heads) return launch_tc<__nv_bfloat16, 2, false>(p, mq, mk, mv, mvp, mo, stream);
+  if (pair_tiles) return launch_tc<__nv_bfloat16, 2, true>(p, mq, mk, mv, mvp, mo, stream);
+  return launch_tc<__nv_bfloat16, 1, false>(p, mq, mk, mv, mvp, mo, stream);
 }
 
 }  // namespace pal

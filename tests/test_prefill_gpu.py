@@ -123,3 +123,15 @@ def test_chunked_prefill_config_reduced(pal, cuda):
     """Llama-3-8B chunked causal prefill shape, 3 sequences x 2048 new tokens over ragged history (auto impl)."""
     case = make_prefill_case(0, [0, 4096, 1111], 2048, 32, 8, 128, dtype=torch.bfloat16)
     check(pal, cuda, case, "auto")
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize(
+    "hist,n,hq,hkv",
+    [([0, 300], 256, 4, 4), ([129], 384, 2, 2), ([1000, 0, 64], 300, 3, 3), ([50], 129, 6, 2), ([0], 640, 1, 1), ([17], 128, 5, 5)],
+)
+def test_odd_head_groups_pair_query_tiles(pal, cuda, dtype, hist, n, hq, hkv):
+    """One or three query heads per kv head: the tcgen05 kernel pairs two query tiles of a head in a CTA (odd and even tile
+    counts, a sequence of exactly one tile, with and without history)."""
+    check(pal, cuda, make_prefill_case(7, hist, n, hq, hkv, 128, dtype=dtype), "tcgen05")
+
