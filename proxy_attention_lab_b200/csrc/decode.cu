@@ -15,7 +15,8 @@
 //    tail of a ragged batch short.
 //  * A producer warp walks the page table (32 page ids per coalesced load, one batch prefetched ahead)
 //    and streams each page's contiguous K block and V block (D*TPP*2 bytes each) into a ring of
-//    shared-memory stages with cp.async.bulk + mbarrier transaction counts.  No multicast.
+//    shared-memory stages with cp.async.bulk + mbarrier transaction counts; as many of its lanes as the ring has
+//    stages each issue one page's copies at a time.  No multicast.
 //  * Four consumer warps take the pages round robin.  Per 16 tokens a warp computes
 //        S^T[16 tok x 8 heads] = K[16 tok x D] . Q^T            (mma.sync m16n8k16, A via ldmatrix)
 //        online softmax over tokens (warp shuffles across the 8 token lanes)
@@ -205,9 +206,13 @@ __global__ void __launch_bounds__(kDecodeThreads, 2) paged_decode_kernel(const D
         const uint32_t pid_cur = pid_next;
         if (j0 + 32 + lane < npg) pid_next = row[j0 + 32 + lane];
         const int cnt = min(32, npg - j0);
-        for (int k = 0; k < cnt; ++k) {
-          uint32_t pid = __shfl_sync(0xffffffffu, pid_cur, k);
-          if (lane == 0 && ok) {
+        // NST consecutive pages go to NST different stages, so NST lanes each take one: wait for the stage, announce
+        // the bytes, issue the two copies.  (A single issuing lane costs ~600 cycles per page, which caps small blocks -
+        // head_dim 32..64 with 16-token pages - far below the memory bandwidth.)
+        for (int b0 = 0; b0 < cnt; b0 += NST) {
+          const int k = b0 + lane;
+          uint32_t pid = __shfl_sync(0xffffffffu, pid_cur, k & 31);
+          if (lane < NST && k < cnt) {
             const uint32_t n = it + j0 + k;
             const uint32_t stage = n % NST;
             ok = mbar_wait(&empty_bar[stage], ((n / NST) & 1) ^ 1, status);
@@ -220,9 +225,9 @@ __global__ void __launch_bounds__(kDecodeThreads, 2) paged_decode_kernel(const D
               bulk_g2s(dst + SM::kBlockBytes, vp + off, SM::kBlockBytes, &full_bar[stage]);
             }
           }
+          ok = __all_sync(0xffffffffu, ok);
+          if (!ok) return;
         }
-        ok = __shfl_sync(0xffffffffu, ok, 0);
-        if (!ok) return;
       }
       // Pad the item to a multiple of four pages with empty hand-shakes, so that local page j always
       // goes to warp j % 4 whatever the CTA processed before: the summation order of a work item, and
