@@ -459,14 +459,13 @@ __global__ void __launch_bounds__(64 + 128 * NQ, 1)
       ok = __shfl_sync(0xffffffffu, ok, 0);
       if (!ok) break;
       if (paged) {
+        // lane i holds page i's id and issues its copy: the pages of a tile go out in parallel, not one after another
         if (lane == 0) mbar_arrive_expect_tx(&k_full[st], npg * kPageBytes);
-        for (int i = 0; i < npg; ++i) {
-          const uint32_t pid = __shfl_sync(0xffffffffu, my_pid, i);
-          if (lane == 0)
-            bulk_g2s(sK + st * kTileBytes + i * kPageBytes,
-                     static_cast<const unsigned char*>(p.k_pool) + ((size_t)pid * p.num_kv_heads + kvh) * kPageBytes,
-                     kPageBytes, &k_full[st]);
-        }
+        __syncwarp();
+        if (lane < npg)
+          bulk_g2s(sK + st * kTileBytes + lane * kPageBytes,
+                   static_cast<const unsigned char*>(p.k_pool) + ((size_t)my_pid * p.num_kv_heads + kvh) * kPageBytes,
+                   kPageBytes, &k_full[st]);
       } else if (lane == 0) {
         const int jd = j - hist_tiles;
         mbar_arrive_expect_tx(&k_full[st], kTileBytes);
@@ -480,11 +479,9 @@ __global__ void __launch_bounds__(64 + 128 * NQ, 1)
       if (!ok) break;
       if (paged) {
         if (lane == 0) mbar_arrive_expect_tx(&v_full[st], npg * kPageBytes);
-        for (int i = 0; i < npg; ++i) {
-          const uint32_t pid = __shfl_sync(0xffffffffu, my_pid, i);
-          if (lane == 0)
-            tma_load_3d(sV + st * kTileBytes + i * kPageBytes, &tm_vpool, 0, 0, (int)(pid * p.num_kv_heads + kvh), &v_full[st]);
-        }
+        __syncwarp();
+        if (lane < npg)
+          tma_load_3d(sV + st * kTileBytes + lane * kPageBytes, &tm_vpool, 0, 0, (int)(my_pid * p.num_kv_heads + kvh), &v_full[st]);
       } else if (lane == 0) {
         const int jd = j - hist_tiles;
         mbar_arrive_expect_tx(&v_full[st], kTileBytes);
