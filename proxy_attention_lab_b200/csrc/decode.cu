@@ -40,7 +40,7 @@ constexpr int kConsumerWarps = 4;
 constexpr int kConsumerThreads = kConsumerWarps * 32;
 constexpr int kDecodeThreads = kConsumerThreads + 32;
 constexpr int kMaxSort = 512;        // rank sequence lengths in-kernel up to this batch size
-constexpr int kHeadsPerItem = 8;     // N of the m16n8k16 MMA
+constexpr int kHeadsPerItem = 8;     // N of the m16n8k16 MMA: one head set; a work item holds HS (1 or 2) of them
 constexpr int kSmemBudget = 113 * 1024;  // per CTA, so that two CTAs fit one SM
 
 struct DecodeParams {
@@ -64,12 +64,13 @@ struct DecodeParams {
   float scale_log2;
 };
 
-template <int D, int TPP>
+template <int D, int TPP, int HS>
 struct DecodeSmem {
   static constexpr int kBlockBytes = D * TPP * 2;       // one (page, kv head) block of K or of V
   static constexpr int kStageBytes = 2 * kBlockBytes;
   static constexpr int kPitch = D + 4;                  // fp32 row pitch of the merge buffer
-  static constexpr int kMergeBytes = kConsumerWarps * kHeadsPerItem * kPitch * 4 + 2 * kConsumerWarps * kHeadsPerItem * 4;
+  static constexpr int kHeads = kHeadsPerItem * HS;     // query heads of one work item
+  static constexpr int kMergeBytes = kConsumerWarps * kHeads * kPitch * 4 + 2 * kConsumerWarps * kHeads * 4;
   static constexpr int kSortBytes = kMaxSort * 4 + kMaxSort * 2;
   static constexpr int kFixedBytes = kMergeBytes + kSortBytes + 1024;
   // A stage is always consumed by warp (stage % 4): the ring length is a multiple of the consumer
@@ -114,9 +115,12 @@ __device__ __forceinline__ void page_range(const DecodeParams& p, int len, int p
   }
 }
 
-template <typename T, int D, int TPP, bool SPLIT, bool APPEND>
+// HS = 2: a work item covers 16 query heads of one kv head (two N = 8 MMA column sets fed from the same K / V fragments),
+// so that groups of more than 8 heads per kv head still read every page once.
+template <typename T, int D, int TPP, bool SPLIT, bool APPEND, int HS>
 __global__ void __launch_bounds__(kDecodeThreads, 2) paged_decode_kernel(const DecodeParams p) {
-  using SM = DecodeSmem<D, TPP>;
+  using SM = DecodeSmem<D, TPP, HS>;
+  constexpr int HPI = SM::kHeads;
   using MMA = Mma16816<T>;
   constexpr int NST = SM::kStages;
   constexpr int KSTEPS = D / 16;
@@ -126,9 +130,9 @@ __global__ void __launch_bounds__(kDecodeThreads, 2) paged_decode_kernel(const D
   extern __shared__ __align__(1024) unsigned char smem[];
   unsigned char* stages = smem;
   float* sm_O = reinterpret_cast<float*>(smem + NST * SM::kStageBytes);
-  float* sm_m = sm_O + kConsumerWarps * kHeadsPerItem * SM::kPitch;
-  float* sm_l = sm_m + kConsumerWarps * kHeadsPerItem;
-  int* sm_len = reinterpret_cast<int*>(sm_l + kConsumerWarps * kHeadsPerItem);
+  float* sm_m = sm_O + kConsumerWarps * HPI * SM::kPitch;
+  float* sm_l = sm_m + kConsumerWarps * HPI;
+  int* sm_len = reinterpret_cast<int*>(sm_l + kConsumerWarps * HPI);
   uint16_t* sm_order = reinterpret_cast<uint16_t*>(sm_len + kMaxSort);
   uint64_t* bars = reinterpret_cast<uint64_t*>(
       (reinterpret_cast<uintptr_t>(sm_order + kMaxSort) + 15) & ~uintptr_t(15));
@@ -267,19 +271,20 @@ __global__ void __launch_bounds__(kDecodeThreads, 2) paged_decode_kernel(const D
     int pb, pe;
     page_range<SPLIT>(p, len, c.part, TPP, pb, pe);
     const int npg = pe - pb;
-    const int head0 = c.kvh * p.group + c.hg * kHeadsPerItem;
-    const int nheads = min(kHeadsPerItem, p.group - c.hg * kHeadsPerItem);
+    const int head0 = c.kvh * p.group + c.hg * HPI;
+    const int nheads = min(HPI, p.group - c.hg * HPI);
 
     // Q^T as the B operand: b0 = Q[head g][16ks + 2t, +1], b1 = Q[head g][16ks + 8 + 2t, +1]
-    uint32_t qf[KSTEPS][2];
-    {
-      const bool valid = g < nheads;
+    uint32_t qf[HS][KSTEPS][2];
+#pragma unroll
+    for (int hs = 0; hs < HS; ++hs) {
+      const bool valid = 8 * hs + g < nheads;
       const uint32_t* qrow =
-          reinterpret_cast<const uint32_t*>(qbase + ((size_t)c.seq * p.num_q_heads + head0 + (valid ? g : 0)) * D);
+          reinterpret_cast<const uint32_t*>(qbase + ((size_t)c.seq * p.num_q_heads + head0 + (valid ? 8 * hs + g : 0)) * D);
 #pragma unroll
       for (int ks = 0; ks < KSTEPS; ++ks) {
-        qf[ks][0] = valid ? qrow[ks * 8 + t] : 0u;
-        qf[ks][1] = valid ? qrow[ks * 8 + 4 + t] : 0u;
+        qf[hs][ks][0] = valid ? qrow[ks * 8 + t] : 0u;
+        qf[hs][ks][1] = valid ? qrow[ks * 8 + 4 + t] : 0u;
       }
     }
     // Append form: the sequence's last token (position len - 1) is not in the pool yet.  The warp that owns its page
@@ -304,11 +309,15 @@ __global__ void __launch_bounds__(kDecodeThreads, 2) paged_decode_kernel(const D
         }
       }
     }
-    float m_run[2] = {-INFINITY, -INFINITY};
-    float l_run[2] = {0.f, 0.f};
-    float o[MTILES][4];
+    float m_run[HS][2], l_run[HS][2];
+    float o[HS][MTILES][4];
 #pragma unroll
-    for (int i = 0; i < MTILES; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+    for (int hs = 0; hs < HS; ++hs) {
+      m_run[hs][0] = m_run[hs][1] = -INFINITY;
+      l_run[hs][0] = l_run[hs][1] = 0.f;
+#pragma unroll
+      for (int i = 0; i < MTILES; ++i) o[hs][i][0] = o[hs][i][1] = o[hs][i][2] = o[hs][i][3] = 0.f;
+    }
 
     // Page n (counted over the whole kernel, items padded to multiples of four) lives in stage n % NST
     // and belongs to warp n % 4; `it` is a multiple of four, so local page j goes to warp j % 4.
@@ -357,8 +366,10 @@ __global__ void __launch_bounds__(kDecodeThreads, 2) paged_decode_kernel(const D
       for (int u = 0; u < UNITS; ++u) {
         const int nvalid = len - (tok0 + 16 * u);
         if (nvalid <= 0) break;
-        // ---- S^T = K . Q^T ----
-        float s[4] = {0.f, 0.f, 0.f, 0.f};
+        // ---- S^T = K . Q^T (the K fragments serve every head set) ----
+        float s[HS][4];
+#pragma unroll
+        for (int hs = 0; hs < HS; ++hs) s[hs][0] = s[hs][1] = s[hs][2] = s[hs][3] = 0.f;
         {
           // matrix i = lane/8: chunk 2ks + (i>>1), tokens 8*(i&1) + lane%8
           const int mi = lane >> 3, r = lane & 7;
@@ -367,51 +378,56 @@ __global__ void __launch_bounds__(kDecodeThreads, 2) paged_decode_kernel(const D
           for (int ks = 0; ks < KSTEPS; ++ks) {
             uint32_t a[4];
             ldmatrix_x4(a, a_lane + ks * 2 * (TPP * 16));
-            MMA::run(s, a, qf[ks][0], qf[ks][1]);
+#pragma unroll
+            for (int hs = 0; hs < HS; ++hs) MMA::run(s[hs], a, qf[hs][ks][0], qf[hs][ks][1]);
           }
         }
-        // s[0],s[1]: token g, heads 2t,2t+1;  s[2],s[3]: token g+8
+        // s[0],s[1]: token g, heads 2t,2t+1 of the set;  s[2],s[3]: token g+8
         const bool v_lo = g < nvalid, v_hi = g + 8 < nvalid;
-        s[0] = v_lo ? s[0] * p.scale_log2 : -INFINITY;
-        s[1] = v_lo ? s[1] * p.scale_log2 : -INFINITY;
-        s[2] = v_hi ? s[2] * p.scale_log2 : -INFINITY;
-        s[3] = v_hi ? s[3] * p.scale_log2 : -INFINITY;
-        float mx0 = fmaxf(s[0], s[2]), mx1 = fmaxf(s[1], s[3]);
+        uint32_t b0[HS], b1[HS], r0[HS], r1[HS];
 #pragma unroll
-        for (int sh = 4; sh <= 16; sh <<= 1) {
-          mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, sh));
-          mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, sh));
-        }
-        const float mn0 = fmaxf(m_run[0], mx0), mn1 = fmaxf(m_run[1], mx1);
-        // token 0 of a processed unit is always valid, so mn0/mn1 are finite here unless the
-        // data itself is non-finite
-        const float c0 = fast_exp2(m_run[0] - mn0), c1 = fast_exp2(m_run[1] - mn1);
-        m_run[0] = mn0;
-        m_run[1] = mn1;
-        const float p0 = fast_exp2(s[0] - mn0), p1 = fast_exp2(s[1] - mn1);
-        const float p2 = fast_exp2(s[2] - mn0), p3 = fast_exp2(s[3] - mn1);
-        l_run[0] = l_run[0] * c0 + p0 + p2;
-        l_run[1] = l_run[1] * c1 + p1 + p3;
-        if (__any_sync(0xffffffffu, c0 != 1.f || c1 != 1.f)) {
+        for (int hs = 0; hs < HS; ++hs) {
+          s[hs][0] = v_lo ? s[hs][0] * p.scale_log2 : -INFINITY;
+          s[hs][1] = v_lo ? s[hs][1] * p.scale_log2 : -INFINITY;
+          s[hs][2] = v_hi ? s[hs][2] * p.scale_log2 : -INFINITY;
+          s[hs][3] = v_hi ? s[hs][3] * p.scale_log2 : -INFINITY;
+          float mx0 = fmaxf(s[hs][0], s[hs][2]), mx1 = fmaxf(s[hs][1], s[hs][3]);
 #pragma unroll
-          for (int i = 0; i < MTILES; ++i) {
-            o[i][0] *= c0;
-            o[i][1] *= c1;
-            o[i][2] *= c0;
-            o[i][3] *= c1;
+          for (int sh = 4; sh <= 16; sh <<= 1) {
+            mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, sh));
+            mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, sh));
+          }
+          const float mn0 = fmaxf(m_run[hs][0], mx0), mn1 = fmaxf(m_run[hs][1], mx1);
+          // token 0 of a processed unit is always valid, so mn0/mn1 are finite here unless the
+          // data itself is non-finite
+          const float c0 = fast_exp2(m_run[hs][0] - mn0), c1 = fast_exp2(m_run[hs][1] - mn1);
+          m_run[hs][0] = mn0;
+          m_run[hs][1] = mn1;
+          const float p0 = fast_exp2(s[hs][0] - mn0), p1 = fast_exp2(s[hs][1] - mn1);
+          const float p2 = fast_exp2(s[hs][2] - mn0), p3 = fast_exp2(s[hs][3] - mn1);
+          l_run[hs][0] = l_run[hs][0] * c0 + p0 + p2;
+          l_run[hs][1] = l_run[hs][1] * c1 + p1 + p3;
+          if (__any_sync(0xffffffffu, c0 != 1.f || c1 != 1.f)) {
+#pragma unroll
+            for (int i = 0; i < MTILES; ++i) {
+              o[hs][i][0] *= c0;
+              o[hs][i][1] *= c1;
+              o[hs][i][2] *= c0;
+              o[hs][i][3] *= c1;
+            }
+          }
+          // P^T as the B operand of the PV MMA.  bf16 keeps only 8 bits of P, so there the residual
+          // P - bf16(P) goes through a second MMA and the product is accurate to ~2^-17.
+          const uint32_t pk0 = MMA::pack(p0, p1), pk1 = MMA::pack(p2, p3);
+          b0[hs] = movmatrix_trans(pk0);
+          b1[hs] = movmatrix_trans(pk1);
+          r0[hs] = r1[hs] = 0;
+          if (MMA::kSplitP) {
+            r0[hs] = movmatrix_trans(MMA::pack_residual(p0, p1, pk0));
+            r1[hs] = movmatrix_trans(MMA::pack_residual(p2, p3, pk1));
           }
         }
-        // P^T as the B operand of the PV MMA.  bf16 keeps only 8 bits of P, so there the residual
-        // P - bf16(P) goes through a second MMA and the product is accurate to ~2^-17.
-        const uint32_t pk0 = MMA::pack(p0, p1), pk1 = MMA::pack(p2, p3);
-        const uint32_t b0 = movmatrix_trans(pk0);
-        const uint32_t b1 = movmatrix_trans(pk1);
-        uint32_t r0 = 0, r1 = 0;
-        if (MMA::kSplitP) {
-          r0 = movmatrix_trans(MMA::pack_residual(p0, p1, pk0));
-          r1 = movmatrix_trans(MMA::pack_residual(p2, p3, pk1));
-        }
-        // ---- O^T += V^T . P^T ----
+        // ---- O^T += V^T . P^T (the V fragments serve every head set) ----
         {
           // matrix i = lane/8: d rows 8*(i&1) + lane%8 of the m-tile, token half i>>1
           const int mi = lane >> 3, r = lane & 7;
@@ -433,8 +449,11 @@ __global__ void __launch_bounds__(kDecodeThreads, 2) paged_decode_kernel(const D
               a[2] &= mask_hi;
               a[3] &= mask_hi;
             }
-            MMA::run(o[mt], a, b0, b1);
-            if (MMA::kSplitP) MMA::run(o[mt], a, r0, r1);
+#pragma unroll
+            for (int hs = 0; hs < HS; ++hs) {
+              MMA::run(o[hs][mt], a, b0[hs], b1[hs]);
+              if (MMA::kSplitP) MMA::run(o[hs][mt], a, r0[hs], r1[hs]);
+            }
           }
         }
       }
@@ -445,24 +464,26 @@ __global__ void __launch_bounds__(kDecodeThreads, 2) paged_decode_kernel(const D
 
     // ---- merge the four warps' partial states ----
 #pragma unroll
-    for (int sh = 4; sh <= 16; sh <<= 1) {
-      l_run[0] += __shfl_xor_sync(0xffffffffu, l_run[0], sh);
-      l_run[1] += __shfl_xor_sync(0xffffffffu, l_run[1], sh);
-    }
-    if (g == 0) {
-      sm_m[warp * kHeadsPerItem + 2 * t] = m_run[0];
-      sm_m[warp * kHeadsPerItem + 2 * t + 1] = m_run[1];
-      sm_l[warp * kHeadsPerItem + 2 * t] = l_run[0];
-      sm_l[warp * kHeadsPerItem + 2 * t + 1] = l_run[1];
-    }
-    {
-      float* ow = sm_O + warp * kHeadsPerItem * SM::kPitch;
+    for (int hs = 0; hs < HS; ++hs) {
+#pragma unroll
+      for (int sh = 4; sh <= 16; sh <<= 1) {
+        l_run[hs][0] += __shfl_xor_sync(0xffffffffu, l_run[hs][0], sh);
+        l_run[hs][1] += __shfl_xor_sync(0xffffffffu, l_run[hs][1], sh);
+      }
+      const int hcol = warp * HPI + 8 * hs + 2 * t;  // this thread's two heads of the set
+      if (g == 0) {
+        sm_m[hcol] = m_run[hs][0];
+        sm_m[hcol + 1] = m_run[hs][1];
+        sm_l[hcol] = l_run[hs][0];
+        sm_l[hcol + 1] = l_run[hs][1];
+      }
+      float* ow = sm_O + hcol * SM::kPitch;
 #pragma unroll
       for (int mt = 0; mt < MTILES; ++mt) {
-        ow[(2 * t) * SM::kPitch + 16 * mt + g] = o[mt][0];
-        ow[(2 * t + 1) * SM::kPitch + 16 * mt + g] = o[mt][1];
-        ow[(2 * t) * SM::kPitch + 16 * mt + g + 8] = o[mt][2];
-        ow[(2 * t + 1) * SM::kPitch + 16 * mt + g + 8] = o[mt][3];
+        ow[16 * mt + g] = o[hs][mt][0];
+        ow[SM::kPitch + 16 * mt + g] = o[hs][mt][1];
+        ow[16 * mt + g + 8] = o[hs][mt][2];
+        ow[SM::kPitch + 16 * mt + g + 8] = o[hs][mt][3];
       }
     }
     // consumer-only barrier built on an mbarrier so that, like every other wait here, it is bounded
@@ -475,7 +496,7 @@ __global__ void __launch_bounds__(kDecodeThreads, 2) paged_decode_kernel(const D
       float M = -INFINITY;
 #pragma unroll
       for (int w = 0; w < kConsumerWarps; ++w) {
-        mw[w] = sm_m[w * kHeadsPerItem + h];
+        mw[w] = sm_m[w * HPI + h];
         M = fmaxf(M, mw[w]);
       }
       float num = 0.f, den = 0.f;
@@ -483,8 +504,8 @@ __global__ void __launch_bounds__(kDecodeThreads, 2) paged_decode_kernel(const D
 #pragma unroll
         for (int w = 0; w < kConsumerWarps; ++w) {
           const float wgt = fast_exp2(mw[w] - M);
-          num += wgt * sm_O[(w * kHeadsPerItem + h) * SM::kPitch + d];
-          den += wgt * sm_l[w * kHeadsPerItem + h];
+          num += wgt * sm_O[(w * HPI + h) * SM::kPitch + d];
+          den += wgt * sm_l[w * HPI + h];
         }
       }
       const size_t row = (size_t)c.seq * p.num_q_heads + head0 + h;
@@ -570,11 +591,11 @@ __global__ void __launch_bounds__(128) lse_combine_kernel(const float* __restric
   }
 }
 
-template <typename T, int D, int TPP, bool SPLIT, bool APPEND>
+template <typename T, int D, int TPP, bool SPLIT, bool APPEND, int HS>
 int launch_decode_inst(const DecodeParams& p, int num_sms, cudaStream_t stream) {
-  using SM = DecodeSmem<D, TPP>;
+  using SM = DecodeSmem<D, TPP, HS>;
   static_assert(SM::kTotalBytes <= 227 * 1024, "decode shared memory exceeds the per-CTA limit");
-  auto kern = paged_decode_kernel<T, D, TPP, SPLIT, APPEND>;
+  auto kern = paged_decode_kernel<T, D, TPP, SPLIT, APPEND, HS>;
   static bool configured[64] = {};
   int dev = 0;
   cudaGetDevice(&dev);
@@ -591,12 +612,12 @@ int launch_decode_inst(const DecodeParams& p, int num_sms, cudaStream_t stream) 
   return (int)cudaGetLastError();
 }
 
-template <typename T, bool SPLIT>
+template <typename T, bool SPLIT, int HS>
 int dispatch_shape(const DecodeParams& p, int head_dim, int tpp, int num_sms, cudaStream_t stream) {
 #define PAL_DECODE_CASE(DD, TT)                                                                        \
   if (head_dim == DD && tpp == TT)                                                                     \
-    return p.new_k ? launch_decode_inst<T, DD, TT, SPLIT, true>(p, num_sms, stream)                    \
-                   : launch_decode_inst<T, DD, TT, SPLIT, false>(p, num_sms, stream);
+    return p.new_k ? launch_decode_inst<T, DD, TT, SPLIT, true, (DD <= 128 ? HS : 1)>(p, num_sms, stream)   \
+                   : launch_decode_inst<T, DD, TT, SPLIT, false, (DD <= 128 ? HS : 1)>(p, num_sms, stream);
   PAL_DECODE_CASE(32, 16)
   PAL_DECODE_CASE(64, 16)
   PAL_DECODE_CASE(80, 16)
@@ -630,6 +651,9 @@ int cached_sm_count() {
 
 size_t align256(size_t x) { return (x + 255) & ~size_t(255); }
 
+// Work items hold 16 query heads when a kv head serves more than 8 (and the accumulators fit: head_dim <= 128), else 8.
+int heads_per_item(int group, int head_dim) { return group > kHeadsPerItem && head_dim <= 128 ? 2 * kHeadsPerItem : kHeadsPerItem; }
+
 }  // namespace
 
 int decode_num_partitions(int max_pages_per_seq, int partition_pages) {
@@ -642,7 +666,8 @@ int decode_num_partitions(int max_pages_per_seq, int partition_pages) {
 // that roughly four items per SM exist, but never smaller than 16 pages.
 int decode_auto_partition_pages(int num_seqs, int num_q_heads, int num_kv_heads, int max_pages_per_seq) {
   const int group = num_q_heads / num_kv_heads;
-  const long long items = (long long)num_seqs * num_kv_heads * ((group + kHeadsPerItem - 1) / kHeadsPerItem);
+  const int hpi = group > kHeadsPerItem ? 2 * kHeadsPerItem : kHeadsPerItem;
+  const long long items = (long long)num_seqs * num_kv_heads * ((group + hpi - 1) / hpi);
   const long long want = 148LL * 4;
   if (items >= 148LL * 2 || max_pages_per_seq <= 32) return 0;
   long long parts = (want + items - 1) / items;
@@ -696,7 +721,8 @@ int launch_decode(const DecodeArgs& a, cudaStream_t stream) {
   p.num_q_heads = a.num_q_heads;
   p.num_kv_heads = a.num_kv_heads;
   p.group = a.num_q_heads / a.num_kv_heads;
-  p.head_groups = (p.group + kHeadsPerItem - 1) / kHeadsPerItem;
+  const int hpi = heads_per_item(p.group, a.head_dim);
+  p.head_groups = (p.group + hpi - 1) / hpi;
   p.max_pages_per_seq = a.max_pages_per_seq;
   p.num_pages = a.num_pages;
   p.partition_pages = a.partition_pages;
@@ -721,11 +747,16 @@ int launch_decode(const DecodeArgs& a, cudaStream_t stream) {
   const int sms = cached_sm_count();
   int rc;
   if (a.dtype == 0)
-    rc = split ? dispatch_shape<__half, true>(p, a.head_dim, a.tokens_per_page, sms, stream)
-               : dispatch_shape<__half, false>(p, a.head_dim, a.tokens_per_page, sms, stream);
+    rc = hpi > kHeadsPerItem ? (split ? dispatch_shape<__half, true, 2>(p, a.head_dim, a.tokens_per_page, sms, stream)
+                                      : dispatch_shape<__half, false, 2>(p, a.head_dim, a.tokens_per_page, sms, stream))
+                             : (split ? dispatch_shape<__half, true, 1>(p, a.head_dim, a.tokens_per_page, sms, stream)
+                                      : dispatch_shape<__half, false, 1>(p, a.head_dim, a.tokens_per_page, sms, stream));
   else
-    rc = split ? dispatch_shape<__nv_bfloat16, true>(p, a.head_dim, a.tokens_per_page, sms, stream)
-               : dispatch_shape<__nv_bfloat16, false>(p, a.head_dim, a.tokens_per_page, sms, stream);
+    rc = hpi > kHeadsPerItem
+             ? (split ? dispatch_shape<__nv_bfloat16, true, 2>(p, a.head_dim, a.tokens_per_page, sms, stream)
+                      : dispatch_shape<__nv_bfloat16, false, 2>(p, a.head_dim, a.tokens_per_page, sms, stream))
+             : (split ? dispatch_shape<__nv_bfloat16, true, 1>(p, a.head_dim, a.tokens_per_page, sms, stream)
+                      : dispatch_shape<__nv_bfloat16, false, 1>(p, a.head_dim, a.tokens_per_page, sms, stream));
   if (rc != 0) return rc;
   if (split) {
     const long long out_rows = (long long)a.num_seqs * a.num_q_heads;
