@@ -135,6 +135,13 @@ __global__ void __launch_bounds__(256) fill_kv_pages_grouped_kernel(
     const long long t0 = grp * kGroupTokens;
     const int ntok = (int)min((long long)kGroupTokens, num_tokens - t0);
     __syncthreads();  // the previous group's shared data is no longer needed
+    // The token rows do not depend on where they go: their staging copies (coalesced 16-byte asynchronous copies, all
+    // in flight at once) are issued first, and the destinations are looked up while they travel.
+    for (int v = threadIdx.x; v < ntok * part_vecs; v += blockDim.x) {
+      const int i = v / part_vecs, in_part = v - i * part_vecs;
+      cp_async_16(sK + i * pitch + in_part * 16, new_keys + (t0 + i) * vec_per_token + vec0 + in_part);
+      cp_async_16(sV + i * pitch + in_part * 16, new_values + (t0 + i) * vec_per_token + vec0 + in_part);
+    }
     if (threadIdx.x < kGroupTokens) {
       long long page = -1;
       int slot = 0;
@@ -163,17 +170,18 @@ __global__ void __launch_bounds__(256) fill_kv_pages_grouped_kernel(
       s_chunk[i] = chunk;
       if (chunk > 1) s_any_wide = 1;
     }
+    asm volatile("cp.async.wait_all;" ::: "memory");
     __syncthreads();
 
     if (!s_any_wide) {
-      // scattered path for this group (same stores as fill_kv_pages_kernel)
+      // scattered path for this group (same stores as fill_kv_pages_kernel, fed from the staged rows)
       for (int v = threadIdx.x; v < ntok * part_vecs; v += blockDim.x) {
-        const int i = v / part_vecs, in_token = vec0 + v - i * part_vecs;
+        const int i = v / part_vecs, in_part = v - i * part_vecs, in_token = vec0 + in_part;
         const long long page = s_page[i];
         if (page < 0) continue;
         const int h = in_token / vec_per_head, c = in_token - h * vec_per_head, slot = s_slot[i];
-        const uint4 kv = new_keys[(t0 + i) * vec_per_token + in_token];
-        const uint4 vv = new_values[(t0 + i) * vec_per_token + in_token];
+        const uint4 kv = *reinterpret_cast<const uint4*>(sK + i * pitch + in_part * 16);
+        const uint4 vv = *reinterpret_cast<const uint4*>(sV + i * pitch + in_part * 16);
         const long long head_base = (page * num_kv_heads + h) * (long long)head_dim * tokens_per_page;
         *reinterpret_cast<uint4*>(k_pool + head_base + ((long long)c * tokens_per_page + slot) * 8) = kv;
         uint16_t* vp = v_pool + head_base + (long long)c * 8 * tokens_per_page + slot;
@@ -187,14 +195,6 @@ __global__ void __launch_bounds__(256) fill_kv_pages_grouped_kernel(
       continue;
     }
 
-    // stage the group's K and V rows: coalesced 16-byte asynchronous copies, all in flight at once
-    for (int v = threadIdx.x; v < ntok * part_vecs; v += blockDim.x) {
-      const int i = v / part_vecs, in_part = v - i * part_vecs;
-      cp_async_16(sK + i * pitch + in_part * 16, new_keys + (t0 + i) * vec_per_token + vec0 + in_part);
-      cp_async_16(sV + i * pitch + in_part * 16, new_values + (t0 + i) * vec_per_token + vec0 + in_part);
-    }
-    asm volatile("cp.async.wait_all;" ::: "memory");
-    __syncthreads();
     // K: consecutive threads take consecutive tokens of one (head, chunk): 16-byte stores that are contiguous
     // in the pool wherever the slots are
     for (int u = threadIdx.x; u < part_vecs * kGroupTokens; u += blockDim.x) {
