@@ -45,7 +45,6 @@
 #include <cuda.h>
 #include <cudaTypedefs.h>
 #include <math.h>
-#include <stdlib.h>
 
 #include "common.cuh"
 #include "launch.h"
@@ -69,25 +68,10 @@ struct TcParams {
   const int32_t* cu_seqlens;  // ragged batches: first row of each sequence; null = every sequence has n_new rows
   void* out;
   unsigned int* status;
-  unsigned int* trace;  // progress markers in host-visible memory; only used by builds with PAL_TC_TRACE
   int num_seqs, n_new, num_q_heads, num_kv_heads, group, max_pages_per_seq;
   long long num_pages;
   float scale_log2;
 };
-
-// Progress marker for fault diagnosis: compiled in only with -DPAL_TC_TRACE, and then active only
-// when the caller supplied a host-visible trace buffer.
-#ifdef PAL_TC_TRACE
-#define PAL_MARK(p, idx, val)                                  \
-  do {                                                         \
-    if ((p).trace != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) { \
-      *reinterpret_cast<volatile unsigned int*>((p).trace + (idx)) = (val); \
-      __threadfence_system();                                  \
-    }                                                          \
-  } while (0)
-#else
-#define PAL_MARK(p, idx, val) do { } while (0)
-#endif
 
 // ---- PTX wrappers ---------------------------------------------------------------------------
 __device__ __forceinline__ void tma_load_4d(void* dst, const CUtensorMap* map, int c0, int c1, int c2, int c3,
@@ -429,7 +413,6 @@ __global__ void __launch_bounds__(64 + 128 * NQ, 1)
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  if (tid == 0) PAL_MARK(p, 0, 1u + tmem_base);
 
   if (warp == 0) {
     // =============================== producer ===============================
@@ -439,7 +422,6 @@ __global__ void __launch_bounds__(64 + 128 * NQ, 1)
       for (int q = 0; q < NQ; ++q)
         for (int kb = 0; kb < 2; ++kb)
           tma_load_4d(sQ + q * kTileBytes + kb * kHalfTileBytes, &tm_q, kb * 64, h0 + q * kHeadStep, row0 + t0 + q * kRowStep, tma_seq, q_full);
-      PAL_MARK(p, 1, 1u);
     }
     for (int j = 0; j < num_tiles && ok; ++j) {
       const int st = j & 1;
@@ -471,7 +453,6 @@ __global__ void __launch_bounds__(64 + 128 * NQ, 1)
         mbar_arrive_expect_tx(&k_full[st], kTileBytes);
         for (int kb = 0; kb < 2; ++kb)
           tma_load_4d(sK + st * kTileBytes + kb * kHalfTileBytes, &tm_k, kb * 64, kvh, row0 + jd * kTile, tma_seq, &k_full[st]);
-        PAL_MARK(p, 2, 1u + j);
       }
       // ---- V ----
       if (lane == 0) ok = mbar_wait(&v_empty[st], par, p.status);
@@ -487,7 +468,6 @@ __global__ void __launch_bounds__(64 + 128 * NQ, 1)
         mbar_arrive_expect_tx(&v_full[st], kTileBytes);
         for (int nb = 0; nb < 2; ++nb)
           tma_load_4d(sV + st * kTileBytes + nb * kHalfTileBytes, &tm_v, nb * 64, kvh, row0 + jd * kTile, tma_seq, &v_full[st]);
-        PAL_MARK(p, 3, 1u + j);
       }
     }
   } else if (warp == 1) {
@@ -512,7 +492,6 @@ __global__ void __launch_bounds__(64 + 128 * NQ, 1)
         v_hist[st] = make_desc(sV_u + st * kTileBytes, 16, 256, kLayoutSw32);
       }
       bool ok = mbar_wait(q_full, 0, p.status);
-      PAL_MARK(p, 4, 1u + ok);
 
       // S_q(j) = Q_q . K(j)^T into TMEM columns [128 q, 128 q + 128)
       auto issue_qk = [&](int q, int j) {
@@ -537,9 +516,7 @@ __global__ void __launch_bounds__(64 + 128 * NQ, 1)
             tc_mma_ss(d_tmem, qa + off, kb + off, idesc_qk128, ks > 0);
           }
         }
-        PAL_MARK(p, 6, 1u + j);
         tc_commit(&s_full[q]);
-        PAL_MARK(p, 7, 1u + j);
       };
       // O_q += P_q(j) . V(j)
       auto issue_pv = [&](int q, int j) {
@@ -561,13 +538,10 @@ __global__ void __launch_bounds__(64 + 128 * NQ, 1)
               tc_mma_ts(d_tmem, a_part + kk * 8, vb + (uint64_t)((kk * 2048) >> 4), idesc_pv_dense, (j > 0 || kk > 0 || part > 0));
           }
         }
-        PAL_MARK(p, 12, 1u + j);
         tc_commit(&o_done[q]);
-        PAL_MARK(p, 13, 1u + j);
       };
 
       if (ok) ok = mbar_wait(&k_full[0], 0, p.status);
-      PAL_MARK(p, 5, 1u + ok);
       if (ok) {
         tc_fence_after();
         for (int q = 0; q < NQ; ++q) issue_qk(q, 0);
@@ -614,7 +588,6 @@ __global__ void __launch_bounds__(64 + 128 * NQ, 1)
       const int jd = j - hist_tiles;
       if (!(ok = mbar_wait(&s_full[q], j & 1, p.status))) break;
       tc_fence_after();
-      if (tid == 64) PAL_MARK(p, 8, 1u + j);
       // which columns need masking at all (warp-uniform), and up to which key offset this row sees
       const bool need_mask = paged ? ((j + 1) * kTile > H) : (jd >= diag || (jd + 1) * kTile > N);
       const int rel_limit = paged ? (H - 1 - j * kTile) : (min(qi, N - 1) - jd * kTile);
@@ -667,7 +640,6 @@ __global__ void __launch_bounds__(64 + 128 * NQ, 1)
           tile_exp_store<T, false, false, false>(tS, p.scale_log2, m_ref, rel_limit, l_run);
       }
       tmem_wait_st();
-      if (tid == 64) PAL_MARK(p, 10, 1u + j);
 
       // The last history tile may hold slots past the history length, and pages that were never
       // loaded: zero those V tokens in shared memory, because 0 * NaN would poison the accumulator.
@@ -687,12 +659,10 @@ __global__ void __launch_bounds__(64 + 128 * NQ, 1)
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&p_full[q]);
-      if (tid == 64) PAL_MARK(p, 11, 1u + j);
     }
 
     // ---- epilogue: O / l -> out[((s*N + qi)*Hq + h0 + q)*D + d] ----
     if (ok) ok = mbar_wait(&o_done[q], (num_tiles - 1) & 1, p.status);
-    if (tid == 64) PAL_MARK(p, 14, 1u + ok);
     // Full tiles (and partial ones of uniform batches, which the tensor map clips at the sequence's end) leave through
     // shared memory: the head's Q tile is no longer read by any MMA, has exactly the size and swizzled layout of the
     // output tile, and two TMA stores write it out in whole lines.  A partial tile of a ragged batch would run into the
@@ -744,7 +714,6 @@ __global__ void __launch_bounds__(64 + 128 * NQ, 1)
   if (warp == 1) {
     tc_fence_after();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512u) : "memory");
-    if (lane == 0) PAL_MARK(p, 16, 1u);
   }
 }
 
@@ -821,10 +790,6 @@ int launch_prefill_tcgen05(const PrefillArgs& a, cudaStream_t stream) {
   p.cu_seqlens = a.cu_seqlens;
   p.out = a.out;
   p.status = &static_cast<WorkspaceHeader*>(a.workspace)->status;
-  p.trace = nullptr;
-#ifdef PAL_TC_TRACE
-  if (const char* t = getenv("PAL_TC_TRACE_PTR")) p.trace = reinterpret_cast<unsigned int*>(strtoull(t, nullptr, 0));
-#endif
   p.num_seqs = a.num_seqs;
   p.n_new = a.tokens_per_seq;
   p.num_q_heads = a.num_q_heads;
