@@ -38,6 +38,12 @@ extern "C" {
 
 #define PAL_DTYPE_F16 0
 #define PAL_DTYPE_BF16 1
+/* OR this into the `dtype` argument of an attention entry point (decode, prefill, lse_combine) to have the
+ * output written as float32 instead of the input type: the arithmetic is unchanged (16-bit inputs, fp32
+ * accumulation), only the final rounding to 16 bits is left out.  No counterpart in the reference, whose
+ * outputs always have the query dtype (src/pal_core/src/ops.cpp:93-94); it exists so that results can be
+ * compared with an fp32 oracle free of output quantisation. */
+#define PAL_OUT_F32 0x100
 
 /* Value of partition_pages that selects the fused single-pass decode kernel, and the value
  * that lets the launcher choose (two-pass when the batch alone cannot fill the GPU). */
@@ -46,6 +52,33 @@ extern "C" {
 
 const char* pal_last_error(void);
 const char* pal_version(void);
+
+/* ---- workspaces --------------------------------------------------------------------------- */
+/* Every attention entry point takes a caller-owned device workspace (256-byte aligned; size from the
+ * *_workspace_bytes functions).  Its first 256 bytes are a header: a work counter for the kernels' dynamic
+ * scheduler and a status word.  The header must be zero before the first call that uses the workspace -
+ * pal_workspace_init (a 256-byte cudaMemsetAsync on `stream`) does that, as does any other memset - and the
+ * kernels leave it zeroed when they finish, so calls that follow one another on a stream need nothing in
+ * between.  One workspace serves one call at a time: calls that may overlap on the GPU need one each.
+ * No counterpart in the reference, where MLX's allocator provides temporaries
+ * (src/pal_core/src/paged_attention_decode_primitive.cpp:163-175). */
+int pal_workspace_init(void* workspace, size_t workspace_bytes, void* stream);
+
+/* Every device-side wait in this library is bounded: when it has lasted `cycles` SM clock cycles the kernel
+ * records PAL_ERR_TIMEOUT in the workspace status word and returns.  Sets the bound for the launches that
+ * follow (process-wide; <= 0 restores the default of 4e9 cycles, about 2 s) and returns the previous one. */
+int64_t pal_set_wait_limit_cycles(int64_t cycles);
+
+/* Reads (with a blocking copy on `stream`) the status word the kernels of the last call that used
+ * `workspace` left there: PAL_OK, or PAL_ERR_TIMEOUT when a bounded device-side wait gave up.  After a
+ * timeout the header is zeroed again, so the workspace can be reused.  Optional; for tests and debugging. */
+int pal_check_status(void* workspace, void* stream);
+
+/* Launches one CTA that waits on a barrier nobody arrives at, bounded to `limit_cycles` (> 0): the wait
+ * expires, the kernel records the timeout in `workspace` and returns normally.  Exists to test the
+ * reporting path of the bounded waits (pal_check_status must then return PAL_ERR_TIMEOUT) without hanging
+ * or faulting anything. */
+int pal_selftest_bounded_wait(void* workspace, int64_t limit_cycles, void* stream);
 
 /* ---- layout helpers ----------------------------------------------------------------------- */
 /* src/pal_core/bindings.cpp:44-46 (get_k_cache_stripe_size) */
@@ -93,7 +126,8 @@ size_t pal_decode_workspace_bytes(int num_seqs, int num_q_heads, int num_kv_head
  * (src/pal_core/src/paged_attention_decode_primitive.cpp:71-266,
  *  src/pal_core/kernels/paged_attention/decode/paged_attention_decode.h.metal:29-412,
  *  src/pal_core/kernels/paged_attention/decode/paged_reduce_decode.h.metal:27-129).
- * queries [>=S, Hq, D] (row s belongs to sequence s), out [S, Hq, D] in the query dtype.
+ * queries [>=S, Hq, D] (row s belongs to sequence s), out [S, Hq, D] in the query dtype (float32 with
+ * dtype | PAL_OUT_F32).
  * A sequence of length <= 0 produces zeros.  scale <= 0 selects 1/sqrt(D).
  * partition_pages: PAL_DECODE_SINGLE_PASS (0) = one fused pass per (sequence, kv head);
  * n > 0 = split every sequence into partitions of n pages, write fp32 (m, l, acc) partials to
@@ -113,8 +147,14 @@ int pal_paged_attention_decode(const void* queries, const void* k_pool, const vo
  * The call allocates nothing.  It fails with PAL_ERR_WORKSPACE when the problem needs more than
  * PAL_STATIC_SCRATCH_BYTES (see pal_decode_workspace_bytes).  All calls on one GPU share the array and
  * it keeps the previous call's contents: calls that overlap on a GPU race, so serialise them.  The first
- * call on each device resolves the array's device address; make that call outside any stream capture. */
+ * call on each device (this one or pal_static_scratch_init) loads the array's module - that is when the
+ * device sets the 16 MiB aside, so it must come before the host commits its last free memory, and it fails
+ * with PAL_ERR_WORKSPACE if the memory is not there - resolves the array's device address and zeroes its
+ * header; make that call outside any stream capture.  pal_check_status_static reads the status word of the
+ * built-in array (see pal_check_status). */
 #define PAL_STATIC_SCRATCH_BYTES (16u * 1024u * 1024u)
+int pal_static_scratch_init(void);
+int pal_check_status_static(void* stream);
 int pal_paged_attention_decode_static(const void* queries, const void* k_pool, const void* v_pool,
                                       const void* page_table, const int32_t* sequence_lengths, void* out,
                                       int num_seqs, int num_q_heads, int num_kv_heads, int head_dim,
@@ -152,6 +192,16 @@ int pal_paged_attention_decode_partials(const void* queries, const void* k_pool,
                                         int partition_pages, void* workspace,
                                         size_t workspace_bytes, void* stream);
 
+/* The same pass with the triple written as one buffer packed_out [S*Hq, D + 2] (fp32): per row D values of acc,
+ * then m, then l - the form a single collective moves between GPUs.  Merge with pal_lse_combine_packed. */
+int pal_paged_attention_decode_partials_packed(const void* queries, const void* k_pool, const void* v_pool,
+                                               const void* page_table, const int32_t* sequence_lengths,
+                                               float* packed_out, int num_seqs, int num_q_heads,
+                                               int num_kv_heads, int head_dim, int tokens_per_page,
+                                               int64_t num_pages, int max_pages_per_seq, float scale,
+                                               int dtype, int partition_pages, void* workspace,
+                                               size_t workspace_bytes, void* stream);
+
 /* Log-sum-exp merge of num_parts partial triples per row (paged_reduce_decode.h.metal:79-128,
  * with fp32 un-normalised partials instead of the reference's 16-bit pre-normalised ones):
  * m, l are [num_parts, rows] and acc is [num_parts, rows, D] (part-major, the layout an
@@ -159,8 +209,14 @@ int pal_paged_attention_decode_partials(const void* queries, const void* k_pool,
  * all empty becomes zeros. */
 int pal_lse_combine(const float* m, const float* l, const float* acc, void* out, int num_parts,
                     int64_t rows, int head_dim, int dtype, void* stream);
+/* The same merge reading packed [num_parts, rows, D + 2] (what an all-gather of the per-GPU packed_out buffers
+ * of pal_paged_attention_decode_partials_packed produces), without unpacking. */
+int pal_lse_combine_packed(const float* packed, void* out, int num_parts, int64_t rows, int head_dim,
+                           int dtype, void* stream);
 
 /* ---- paged_attention_prefill -------------------------------------------------------------- */
+/* The prefill kernels need the 256-byte workspace header only: this returns 256 for every problem (the
+ * arguments are there so that the answer can depend on them later without an ABI change). */
 size_t pal_prefill_workspace_bytes(int num_seqs, int tokens_per_seq, int num_q_heads,
                                    int num_kv_heads, int head_dim);
 
@@ -170,6 +226,7 @@ size_t pal_prefill_workspace_bytes(int num_seqs, int tokens_per_seq, int num_q_h
  * q_prompt [S*N, Hq, D], k_prompt / v_prompt [S*N, Hkv, D] dense (sequence-major, then token);
  * history_lens[s] tokens of history are read from the pages; out [S*N*Hq, D], row
  * (s*N + i)*Hq + h.  Query i sees all history tokens and new tokens 0..i.
+ * dtype may carry PAL_OUT_F32 (float32 output).
  * impl: 0 = let the launcher choose, 1 = mma.sync kernel (every supported shape),
  * 2 = tcgen05/TMEM kernel (D = 128, TPP = 16 only; PAL_ERR_UNSUPPORTED otherwise). */
 int pal_paged_attention_prefill(const void* q_prompt, const void* k_prompt, const void* v_prompt,
@@ -195,11 +252,6 @@ int pal_paged_attention_prefill_ragged(const void* q_prompt, const void* k_promp
                                        int num_kv_heads, int head_dim, int tokens_per_page, int64_t num_pages,
                                        int max_pages_per_seq, float scale, int dtype, int impl, void* workspace,
                                        size_t workspace_bytes, void* stream);
-
-/* Reads (with a blocking copy on `stream`) the status word the kernels of the last call that
- * used `workspace` left there: PAL_OK, or PAL_ERR_TIMEOUT when a bounded device-side wait gave
- * up.  Optional; intended for tests and debugging. */
-int pal_check_status(const void* workspace, void* stream);
 
 #ifdef __cplusplus
 }

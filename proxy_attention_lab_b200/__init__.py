@@ -11,7 +11,9 @@ from .ops import (  # noqa: F401
     get_k_cache_stripe_size,
     get_optimal_page_size,
     get_v_cache_shape,
+    check_status,
     lse_combine,
+    lse_combine_packed,
     paged_attention,
     paged_attention_decode,
     paged_attention_decode_append,
@@ -26,7 +28,9 @@ __all__ = [
     "get_k_cache_stripe_size",
     "get_optimal_page_size",
     "get_v_cache_shape",
+    "check_status",
     "lse_combine",
+    "lse_combine_packed",
     "paged_attention",
     "paged_attention_decode",
     "paged_attention_decode_append",

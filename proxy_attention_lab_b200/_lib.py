@@ -7,12 +7,10 @@ declares, importing this module raises.  Build it with ``python proxy_attention_
 from __future__ import annotations
 
 import ctypes
-import os
 from ctypes import c_char_p, c_float, c_int, c_int64, c_size_t, c_void_p
 from pathlib import Path
 
-# PAL_B200_LIB selects another build of the library (for A/B comparisons of kernel variants)
-LIB_PATH = Path(os.environ.get("PAL_B200_LIB") or (Path(__file__).resolve().parent / "libpal_b200.so"))
+LIB_PATH = Path(__file__).resolve().parent / "libpal_b200.so"
 
 PAL_OK = 0
 PAL_ERR_BAD_ARG = -1
@@ -23,6 +21,8 @@ PAL_ERR_TIMEOUT = -5
 
 PAL_DTYPE_F16 = 0
 PAL_DTYPE_BF16 = 1
+PAL_OUT_F32 = 0x100
+PAL_STATIC_SCRATCH_BYTES = 16 * 1024 * 1024
 
 PAL_DECODE_SINGLE_PASS = 0
 PAL_DECODE_AUTO = -1
@@ -65,7 +65,17 @@ SIGNATURES = {
         c_int,
         [_P, _P, _P, _P, _P, _P, _P, _P, _P, c_int, c_int64, c_int, c_int, c_int, c_int, c_int, c_int64, c_int, c_float, c_int, c_int, _P, c_size_t, _P],
     ),
+    "pal_paged_attention_decode_partials_packed": (
+        c_int,
+        [_P, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int64, c_int, c_float, c_int, c_int, _P, c_size_t, _P],
+    ),
+    "pal_lse_combine_packed": (c_int, [_P, _P, c_int, c_int64, c_int, c_int, _P]),
+    "pal_workspace_init": (c_int, [_P, c_size_t, _P]),
+    "pal_set_wait_limit_cycles": (c_int64, [c_int64]),
+    "pal_selftest_bounded_wait": (c_int, [_P, c_int64, _P]),
     "pal_check_status": (c_int, [_P, _P]),
+    "pal_static_scratch_init": (c_int, []),
+    "pal_check_status_static": (c_int, [_P]),
 }
 
 

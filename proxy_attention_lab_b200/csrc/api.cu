@@ -15,6 +15,9 @@
 namespace pal {
 
 static thread_local char g_error[512] = "";
+static std::atomic<long long> g_wait_limit{kDefaultWaitLimitCycles};
+
+long long wait_limit_cycles() { return g_wait_limit.load(std::memory_order_relaxed); }
 
 void set_error(const char* fmt, ...) {
   va_list ap;
@@ -23,9 +26,13 @@ void set_error(const char* fmt, ...) {
   va_end(ap);
 }
 
-static int cuda_rc(int rc, const char* what) {
+int cuda_rc(int rc, const char* what) {
   if (rc == 0) return PAL_OK;
   if (rc < 0) return rc;  // already a PAL_ERR_* with a message
+  if (rc == (int)cudaErrorMemoryAllocation) {
+    set_error("%s: out of device memory (%s)", what, cudaGetErrorString((cudaError_t)rc));
+    return PAL_ERR_WORKSPACE;
+  }
   set_error("%s: CUDA error %d (%s)", what, rc, cudaGetErrorString((cudaError_t)rc));
   return PAL_ERR_LAUNCH;
 }
@@ -34,6 +41,25 @@ static bool check_dtype(int dtype, const char* what) {
   if (dtype == PAL_DTYPE_F16 || dtype == PAL_DTYPE_BF16) return true;
   set_error("%s: dtype %d is not supported (0 = float16, 1 = bfloat16)", what, dtype);
   return false;
+}
+
+// The attention entry points take the element type with PAL_OUT_F32 optionally OR'ed in.
+static bool split_dtype(int dtype_arg, const char* what, int* dtype, bool* out_f32) {
+  *out_f32 = (dtype_arg & PAL_OUT_F32) != 0;
+  *dtype = dtype_arg & ~PAL_OUT_F32;
+  return check_dtype(*dtype, what);
+}
+
+// One CTA that waits on an mbarrier nobody ever arrives at: the wait runs into its limit, records the
+// timeout in the workspace status word and the kernel returns normally.
+__global__ void bounded_wait_selftest_kernel(WorkspaceHeader* hdr, long long limit_cycles) {
+  __shared__ uint64_t bar;
+  if (threadIdx.x == 0) {
+    mbar_init(&bar, 1);
+    fence_mbar_init();
+    const WaitCtx ctx{&hdr->status, limit_cycles};
+    mbar_wait(&bar, 0, ctx);
+  }
 }
 
 static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
@@ -180,7 +206,7 @@ size_t pal_decode_workspace_bytes(int num_seqs, int num_q_heads, int num_kv_head
 }
 
 static int decode_common(DecodeArgs& a, void* stream, const char* what) {
-  if (!check_dtype(a.dtype, what)) return PAL_ERR_UNSUPPORTED;
+  if (!split_dtype(a.dtype, what, &a.dtype, &a.out_f32)) return PAL_ERR_UNSUPPORTED;
   int rc = check_heads(what, a.num_q_heads, a.num_kv_heads, a.head_dim, a.tokens_per_page);
   if (rc != PAL_OK) return rc;
   if (a.num_seqs < 0 || a.num_pages < 0 || a.max_pages_per_seq < 0) {
@@ -200,7 +226,7 @@ static int decode_common(DecodeArgs& a, void* stream, const char* what) {
   if (a.partition_pages < 0)
     a.partition_pages =
         decode_auto_partition_pages(a.num_seqs, a.num_q_heads, a.num_kv_heads, a.max_pages_per_seq);
-  if (a.max_pages_per_seq == 0) a.partition_pages = a.m_out ? 1 : 0;
+  if (a.max_pages_per_seq == 0) a.partition_pages = (a.m_out || a.packed_out) ? 1 : 0;
   const size_t need = decode_workspace_bytes(a.num_seqs, a.num_q_heads, a.num_kv_heads, a.head_dim,
                                              a.tokens_per_page, a.max_pages_per_seq, a.partition_pages);
   if (!a.workspace || a.workspace_bytes < need || (reinterpret_cast<uintptr_t>(a.workspace) & 255)) {
@@ -319,23 +345,80 @@ int pal_paged_attention_decode_partials(const void* queries, const void* k_pool,
   return decode_common(a, stream, "paged_attention_decode_partials");
 }
 
-int pal_lse_combine(const float* m, const float* l, const float* acc, void* out, int num_parts, int64_t rows,
-                    int head_dim, int dtype, void* stream) {
-  if (!check_dtype(dtype, "lse_combine")) return PAL_ERR_UNSUPPORTED;
+int pal_paged_attention_decode_partials_packed(const void* queries, const void* k_pool, const void* v_pool,
+                                               const void* page_table, const int32_t* sequence_lengths,
+                                               float* packed_out, int num_seqs, int num_q_heads, int num_kv_heads,
+                                               int head_dim, int tokens_per_page, int64_t num_pages,
+                                               int max_pages_per_seq, float scale, int dtype, int partition_pages,
+                                               void* workspace, size_t workspace_bytes, void* stream) {
+  DecodeArgs a{};
+  a.queries = queries;
+  a.k_pool = k_pool;
+  a.v_pool = v_pool;
+  a.page_table = static_cast<const uint32_t*>(page_table);
+  a.sequence_lengths = sequence_lengths;
+  a.out = nullptr;
+  a.packed_out = packed_out;
+  a.num_seqs = num_seqs;
+  a.num_q_heads = num_q_heads;
+  a.num_kv_heads = num_kv_heads;
+  a.head_dim = head_dim;
+  a.tokens_per_page = tokens_per_page;
+  a.num_pages = num_pages;
+  a.max_pages_per_seq = max_pages_per_seq;
+  a.scale = scale;
+  a.dtype = dtype;
+  a.partition_pages = partition_pages;
+  a.workspace = workspace;
+  a.workspace_bytes = workspace_bytes;
+  if (partition_pages <= 0) {
+    set_error("paged_attention_decode_partials_packed: partition_pages must be > 0");
+    return PAL_ERR_BAD_ARG;
+  }
+  if (num_seqs > 0 && !packed_out) {
+    set_error("paged_attention_decode_partials_packed: null output pointer");
+    return PAL_ERR_BAD_ARG;
+  }
+  return decode_common(a, stream, "paged_attention_decode_partials_packed");
+}
+
+static int combine_common(const char* what, const PartialsView& in, void* out, int num_parts, int64_t rows, int head_dim,
+                          int dtype_arg, void* stream) {
+  int dtype;
+  bool out_f32;
+  if (!split_dtype(dtype_arg, what, &dtype, &out_f32)) return PAL_ERR_UNSUPPORTED;
   if (num_parts <= 0 || rows < 0 || head_dim <= 0) {
-    set_error("lse_combine: num_parts and head_dim must be positive, rows non-negative");
+    set_error("%s: num_parts and head_dim must be positive, rows non-negative", what);
     return PAL_ERR_BAD_ARG;
   }
   if (rows == 0) return PAL_OK;
-  if (!m || !l || !acc || !out) {
-    set_error("lse_combine: null pointer");
+  if (rows > 0x7fffffffLL) {
+    set_error("%s: rows must be below 2^31", what);
     return PAL_ERR_BAD_ARG;
   }
-  return cuda_rc(launch_lse_combine(m, l, acc, out, nullptr, nullptr, nullptr, num_parts, rows, head_dim, dtype, rows,
-                                    1, rows * head_dim, head_dim, (cudaStream_t)stream),
-                 "lse_combine");
+  if (!in.m || !in.l || !in.acc || !out) {
+    set_error("%s: null pointer", what);
+    return PAL_ERR_BAD_ARG;
+  }
+  return cuda_rc(launch_lse_combine(in, out, out_f32, TripleOut{}, num_parts, rows, head_dim, dtype, (cudaStream_t)stream), what);
 }
 
+int pal_lse_combine(const float* m, const float* l, const float* acc, void* out, int num_parts, int64_t rows,
+                    int head_dim, int dtype, void* stream) {
+  const PartialsView in{m, l, acc, rows, 1, rows * head_dim, head_dim};
+  return combine_common("lse_combine", in, out, num_parts, rows, head_dim, dtype, stream);
+}
+
+int pal_lse_combine_packed(const float* packed, void* out, int num_parts, int64_t rows, int head_dim, int dtype,
+                           void* stream) {
+  const long long pitch = head_dim + 2;
+  const PartialsView in{packed ? packed + head_dim : nullptr, packed ? packed + head_dim + 1 : nullptr, packed,
+                        rows * pitch, pitch, rows * pitch, pitch};
+  return combine_common("lse_combine_packed", in, out, num_parts, rows, head_dim, dtype, stream);
+}
+
+// The prefill kernels keep everything in shared memory and TMEM: the workspace is only the 256-byte header with the
+// status word, whatever the problem size (the arguments exist so that a later kernel may need more without an ABI change).
 size_t pal_prefill_workspace_bytes(int num_seqs, int tokens_per_seq, int num_q_heads, int num_kv_heads,
                                    int head_dim) {
   (void)num_seqs;
@@ -351,9 +434,11 @@ static int prefill_common(const char* what, const void* q_prompt, const void* k_
                           const void* k_pool, const void* v_pool, const void* page_table, const int32_t* history_lens,
                           const int32_t* cu_seqlens, int64_t total_tokens, void* out, int num_seqs, int tokens_per_seq,
                           int num_q_heads, int num_kv_heads, int head_dim, int tokens_per_page, int64_t num_pages,
-                          int max_pages_per_seq, float scale, int dtype, int impl, void* workspace,
+                          int max_pages_per_seq, float scale, int dtype_arg, int impl, void* workspace,
                           size_t workspace_bytes, void* stream) {
-  if (!check_dtype(dtype, what)) return PAL_ERR_UNSUPPORTED;
+  int dtype;
+  bool out_f32;
+  if (!split_dtype(dtype_arg, what, &dtype, &out_f32)) return PAL_ERR_UNSUPPORTED;
   int rc = check_heads(what, num_q_heads, num_kv_heads, head_dim, tokens_per_page);
   if (rc != PAL_OK) return rc;
   if (num_seqs < 0 || tokens_per_seq < 0 || num_pages < 0 || max_pages_per_seq < 0) {
@@ -385,6 +470,7 @@ static int prefill_common(const char* what, const void* q_prompt, const void* k_
   a.cu_seqlens = cu_seqlens;
   a.total_tokens = total_tokens;
   a.out = out;
+  a.out_f32 = out_f32;
   a.num_seqs = num_seqs;
   a.tokens_per_seq = tokens_per_seq;
   a.num_q_heads = num_q_heads;
@@ -446,7 +532,33 @@ int pal_paged_attention_prefill_ragged(const void* q_prompt, const void* k_promp
                         num_pages, max_pages_per_seq, scale, dtype, impl, workspace, workspace_bytes, stream);
 }
 
-int pal_check_status(const void* workspace, void* stream) {
+int pal_workspace_init(void* workspace, size_t workspace_bytes, void* stream) {
+  if (!workspace || workspace_bytes < sizeof(WorkspaceHeader) || (reinterpret_cast<uintptr_t>(workspace) & 255)) {
+    set_error("workspace_init: a 256-byte aligned workspace of at least %zu bytes is required", sizeof(WorkspaceHeader));
+    return PAL_ERR_WORKSPACE;
+  }
+  return cuda_rc((int)cudaMemsetAsync(workspace, 0, sizeof(WorkspaceHeader), (cudaStream_t)stream), "workspace_init");
+}
+
+int64_t pal_set_wait_limit_cycles(int64_t cycles) {
+  if (cycles <= 0) cycles = kDefaultWaitLimitCycles;
+  return g_wait_limit.exchange(cycles, std::memory_order_relaxed);
+}
+
+int pal_selftest_bounded_wait(void* workspace, int64_t limit_cycles, void* stream) {
+  if (!workspace || (reinterpret_cast<uintptr_t>(workspace) & 255)) {
+    set_error("selftest_bounded_wait: a 256-byte aligned workspace is required");
+    return PAL_ERR_WORKSPACE;
+  }
+  if (limit_cycles <= 0 || limit_cycles > kDefaultWaitLimitCycles) {
+    set_error("selftest_bounded_wait: limit_cycles must be in (0, %lld]", kDefaultWaitLimitCycles);
+    return PAL_ERR_BAD_ARG;
+  }
+  bounded_wait_selftest_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(static_cast<WorkspaceHeader*>(workspace), limit_cycles);
+  return cuda_rc((int)cudaGetLastError(), "selftest_bounded_wait");
+}
+
+int pal_check_status(void* workspace, void* stream) {
   if (!workspace) {
     set_error("check_status: workspace is null");
     return PAL_ERR_BAD_ARG;
@@ -456,6 +568,9 @@ int pal_check_status(const void* workspace, void* stream) {
   if (e == cudaSuccess) e = cudaStreamSynchronize((cudaStream_t)stream);
   if (e != cudaSuccess) return cuda_rc((int)e, "check_status");
   if (h.status == kStatusTimeout) {
+    // a kernel that gave up left the scheduler's counters wherever they were: make the workspace usable again
+    e = cudaMemsetAsync(workspace, 0, sizeof(WorkspaceHeader), (cudaStream_t)stream);
+    if (e != cudaSuccess) return cuda_rc((int)e, "check_status");
     set_error("a bounded device-side wait timed out");
     return PAL_ERR_TIMEOUT;
   }

@@ -13,18 +13,28 @@
 
 namespace pal {
 
-// Layout of the first 256 bytes of every workspace.
+// Layout of the first 256 bytes of every workspace.  The caller zeroes it once (pal_workspace_init, or any
+// memset of the first 256 bytes); every kernel that uses the counters puts them back to zero before it
+// ends, so calls that follow one another on a stream need no memset in between.
 struct WorkspaceHeader {
-  unsigned int work_counter;   // dynamic work-item scheduler (zeroed by the launcher)
-  unsigned int status;         // 0 = ok, otherwise a PAL_ERR_* code negated to positive
-  unsigned int reserved[62];
+  unsigned int work_counter;   // dynamic work-item scheduler; the last CTA to finish resets it
+  unsigned int status;         // 0 = ok, otherwise a PAL_ERR_* code negated to positive (sticky until read)
+  unsigned int done_counter;   // CTAs that have finished; the last one resets both counters
+  unsigned int reserved[61];
 };
 static_assert(sizeof(WorkspaceHeader) == 256, "workspace header is 256 bytes");
 
 constexpr unsigned int kStatusTimeout = 5;  // -PAL_ERR_TIMEOUT
 
-// Upper bound, in SM clock cycles, for any single device-side wait (about 2 s at 2 GHz).
-constexpr long long kSpinLimitCycles = 4000000000LL;
+// Default upper bound, in SM clock cycles, for any single device-side wait (about 2 s at 2 GHz);
+// pal_set_wait_limit_cycles replaces it for the launches that follow.
+constexpr long long kDefaultWaitLimitCycles = 4000000000LL;
+
+// Where a bounded wait reports to, and how long it may last.
+struct WaitCtx {
+  unsigned int* status;
+  long long limit_cycles;
+};
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));
@@ -56,15 +66,15 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   return ok != 0;
 }
 // Bounded wait: returns false (after recording a timeout in *status) instead of spinning forever.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, unsigned int* status) {
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, const WaitCtx& ctx) {
   if (mbar_try_wait(bar, parity)) return true;
   const long long t0 = clock64();
   for (;;) {
 #pragma unroll 1
     for (int i = 0; i < 256; ++i)
       if (mbar_try_wait(bar, parity)) return true;
-    if (clock64() - t0 > kSpinLimitCycles) {
-      if (status) atomicExch(status, kStatusTimeout);
+    if (clock64() - t0 > ctx.limit_cycles) {
+      if (ctx.status) atomicExch(ctx.status, kStatusTimeout);
       return false;
     }
   }

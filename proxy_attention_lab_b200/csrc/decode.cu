@@ -56,6 +56,8 @@ struct DecodeParams {
   float* part_l;
   float* part_acc;
   WorkspaceHeader* hdr;
+  long long wait_limit;  // cycles any single device-side wait may last
+  int out_f32;           // out is float32 instead of the query dtype
   int num_seqs, num_q_heads, num_kv_heads, group, head_groups;
   int max_pages_per_seq;
   long long num_pages;
@@ -146,7 +148,7 @@ __global__ void __launch_bounds__(kDecodeThreads, 2) paged_decode_kernel(const D
   const int tid = threadIdx.x;
   const int warp = tid >> 5;
   const int lane = tid & 31;
-  unsigned int* status = &p.hdr->status;
+  const WaitCtx status{&p.hdr->status, p.wait_limit};
 
   if (tid == 0) {
     for (int i = 0; i < NST; ++i) {
@@ -248,6 +250,15 @@ __global__ void __launch_bounds__(kDecodeThreads, 2) paged_decode_kernel(const D
       ok = __shfl_sync(0xffffffffu, ok, 0);
       if (!ok) return;
       it += npg_pad;
+    }
+    // Every CTA has drawn its last item before it gets here, so the CTA that arrives last can put the scheduler's
+    // counters back to zero for the next launch that uses this workspace.
+    if (lane == 0) {
+      __threadfence();
+      if (atomicAdd(&p.hdr->done_counter, 1u) == gridDim.x - 1) {
+        p.hdr->work_counter = 0u;
+        p.hdr->done_counter = 0u;
+      }
     }
     return;
   }
@@ -517,7 +528,11 @@ __global__ void __launch_bounds__(kDecodeThreads, 2) paged_decode_kernel(const D
           p.part_l[prow] = den;
         }
       } else {
-        static_cast<T*>(p.out)[row * D + d] = MMA::from_float(den > 0.f ? num / den : 0.f);
+        const float val = den > 0.f ? num / den : 0.f;
+        if (p.out_f32)
+          static_cast<float*>(p.out)[row * D + d] = val;
+        else
+          static_cast<T*>(p.out)[row * D + d] = MMA::from_float(val);
       }
     }
     __syncwarp();
@@ -529,22 +544,19 @@ __global__ void __launch_bounds__(kDecodeThreads, 2) paged_decode_kernel(const D
 
 // Merge num_parts partial triples per row.  One CTA per row, one thread per head-dim element pair.
 // m/l/acc are addressed with explicit strides so the same kernel serves the in-workspace layout
-// [row][part] and the part-major layout [part][row] of gathered per-GPU triples.
+// [row][part], the part-major layout [part][row] of gathered per-GPU triples and the packed layout
+// [part][row][D + 2] (acc, m, l in one row) that a single collective moves.
 template <typename T>
-__global__ void __launch_bounds__(128) lse_combine_kernel(const float* __restrict__ m, const float* __restrict__ l,
-                                                          const float* __restrict__ acc, T* __restrict__ out,
-                                                          float* __restrict__ m_out, float* __restrict__ l_out,
-                                                          float* __restrict__ acc_out, int num_parts, int head_dim,
-                                                          long long part_stride_ml, long long row_stride_ml,
-                                                          long long part_stride_acc, long long row_stride_acc) {
+__global__ void __launch_bounds__(128) lse_combine_kernel(const PartialsView in, void* __restrict__ out, int out_f32,
+                                                          const TripleOut triple, int num_parts, int head_dim) {
   const long long row = blockIdx.x;
-  const float* mr = m + row * row_stride_ml;
-  const float* lr = l + row * row_stride_ml;
+  const float* mr = in.m + row * in.row_stride_ml;
+  const float* lr = in.l + row * in.row_stride_ml;
   __shared__ float s_w[1024];
   __shared__ float s_red[8];
   // pass 1: global max over partitions
   float mx = -INFINITY;
-  for (int j = threadIdx.x; j < num_parts; j += blockDim.x) mx = fmaxf(mx, mr[j * part_stride_ml]);
+  for (int j = threadIdx.x; j < num_parts; j += blockDim.x) mx = fmaxf(mx, mr[j * in.part_stride_ml]);
 #pragma unroll
   for (int sh = 16; sh >= 1; sh >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, sh));
   if ((threadIdx.x & 31) == 0) s_red[threadIdx.x >> 5] = mx;
@@ -555,10 +567,10 @@ __global__ void __launch_bounds__(128) lse_combine_kernel(const float* __restric
   // pass 2: weights and denominator
   float den = 0.f;
   for (int j = threadIdx.x; j < num_parts; j += blockDim.x) {
-    const float mj = mr[j * part_stride_ml];
+    const float mj = mr[j * in.part_stride_ml];
     const float w = (mj > -INFINITY) ? __expf(mj - M) : 0.f;
     if (j < 1024) s_w[j] = w;
-    den += w * lr[j * part_stride_ml];
+    den += w * lr[j * in.part_stride_ml];
   }
 #pragma unroll
   for (int sh = 16; sh >= 1; sh >>= 1) den += __shfl_xor_sync(0xffffffffu, den, sh);
@@ -566,7 +578,7 @@ __global__ void __launch_bounds__(128) lse_combine_kernel(const float* __restric
   __syncthreads();
   float den_all = 0.f;
   for (int w = 0; w < (int)(blockDim.x >> 5); ++w) den_all += s_red[w];
-  const float* ar = acc + row * row_stride_acc;
+  const float* ar = in.acc + row * in.row_stride_acc;
   for (int d = threadIdx.x; d < head_dim; d += blockDim.x) {
     float num = 0.f;
     for (int j = 0; j < num_parts; ++j) {
@@ -574,20 +586,23 @@ __global__ void __launch_bounds__(128) lse_combine_kernel(const float* __restric
       if (j < 1024) {
         w = s_w[j];
       } else {
-        const float mj = mr[j * part_stride_ml];
+        const float mj = mr[j * in.part_stride_ml];
         w = (mj > -INFINITY) ? __expf(mj - M) : 0.f;
       }
-      if (w != 0.f) num += w * ar[j * part_stride_acc + d];
+      if (w != 0.f) num += w * ar[j * in.part_stride_acc + d];
     }
     if (out) {
       const float v = den_all > 0.f ? num / den_all : 0.f;
-      out[row * head_dim + d] = Mma16816<T>::from_float(v);
+      if (out_f32)
+        static_cast<float*>(out)[row * head_dim + d] = v;
+      else
+        static_cast<T*>(out)[row * head_dim + d] = Mma16816<T>::from_float(v);
     }
-    if (acc_out) acc_out[row * head_dim + d] = num;
+    if (triple.acc) triple.acc[row * triple.row_stride_acc + d] = num;
   }
-  if (threadIdx.x == 0 && m_out) {
-    m_out[row] = M;
-    l_out[row] = den_all;
+  if (threadIdx.x == 0 && triple.m) {
+    triple.m[row * triple.row_stride_ml] = M;
+    triple.l[row * triple.row_stride_ml] = den_all;
   }
 }
 
@@ -596,14 +611,10 @@ int launch_decode_inst(const DecodeParams& p, int num_sms, cudaStream_t stream) 
   using SM = DecodeSmem<D, TPP, HS>;
   static_assert(SM::kTotalBytes <= 227 * 1024, "decode shared memory exceeds the per-CTA limit");
   auto kern = paged_decode_kernel<T, D, TPP, SPLIT, APPEND, HS>;
-  static bool configured[64] = {};
-  int dev = 0;
-  cudaGetDevice(&dev);
-  if (dev < 64 && !configured[dev]) {
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SM::kTotalBytes);
-    if (e != cudaSuccess) return (int)e;
-    configured[dev] = true;
-  }
+  static DeviceOnce configured;  // one per instantiation
+  const int rc = configured.run(
+      [&] { return (int)cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SM::kTotalBytes); });
+  if (rc != 0) return rc;
   const int ctas_per_sm = SM::kTotalBytes <= kSmemBudget ? 2 : 1;
   int grid = num_sms * ctas_per_sm;
   if (grid > p.num_items) grid = p.num_items;
@@ -636,25 +647,24 @@ int dispatch_shape(const DecodeParams& p, int head_dim, int tpp, int num_sms, cu
   return -2;
 }
 
-int cached_sm_count() {
-  static int sms[64] = {};
-  int dev = 0;
-  cudaGetDevice(&dev);
-  if (dev >= 64) return 148;
-  if (sms[dev] == 0) {
-    int n = 0;
-    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
-    sms[dev] = n;
-  }
-  return sms[dev];
-}
-
 size_t align256(size_t x) { return (x + 255) & ~size_t(255); }
 
 // Work items hold 16 query heads when a kv head serves more than 8 (and the accumulators fit: head_dim <= 128), else 8.
 int heads_per_item(int group, int head_dim) { return group > kHeadsPerItem && head_dim <= 128 ? 2 * kHeadsPerItem : kHeadsPerItem; }
 
 }  // namespace
+
+int cached_sm_count() {
+  static std::atomic<int> sms[kMaxDevices] = {};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return 148;
+  int n = sms[dev].load(std::memory_order_relaxed);
+  if (n == 0) {
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+    sms[dev].store(n, std::memory_order_relaxed);  // every thread computes the same value
+  }
+  return n;
+}
 
 int decode_num_partitions(int max_pages_per_seq, int partition_pages) {
   if (partition_pages <= 0) return 1;
@@ -690,19 +700,14 @@ size_t decode_workspace_bytes(int num_seqs, int num_q_heads, int num_kv_heads, i
   return bytes;
 }
 
-int launch_lse_combine(const float* m, const float* l, const float* acc, void* out, float* m_out, float* l_out,
-                       float* acc_out, int num_parts, long long rows, int head_dim, int dtype, long long part_stride_ml,
-                       long long row_stride_ml, long long part_stride_acc, long long row_stride_acc,
-                       cudaStream_t stream) {
+int launch_lse_combine(const PartialsView& in, void* out, bool out_f32, const TripleOut& triple, int num_parts,
+                       long long rows, int head_dim, int dtype, cudaStream_t stream) {
   if (rows == 0) return 0;
   if (dtype == 0)
-    lse_combine_kernel<__half><<<(unsigned)rows, 128, 0, stream>>>(m, l, acc, (__half*)out, m_out, l_out, acc_out,
-                                                                   num_parts, head_dim, part_stride_ml, row_stride_ml,
-                                                                   part_stride_acc, row_stride_acc);
+    lse_combine_kernel<__half><<<(unsigned)rows, 128, 0, stream>>>(in, out, out_f32 ? 1 : 0, triple, num_parts, head_dim);
   else
-    lse_combine_kernel<__nv_bfloat16><<<(unsigned)rows, 128, 0, stream>>>(
-        m, l, acc, (__nv_bfloat16*)out, m_out, l_out, acc_out, num_parts, head_dim, part_stride_ml, row_stride_ml,
-        part_stride_acc, row_stride_acc);
+    lse_combine_kernel<__nv_bfloat16><<<(unsigned)rows, 128, 0, stream>>>(in, out, out_f32 ? 1 : 0, triple, num_parts,
+                                                                         head_dim);
   return (int)cudaGetLastError();
 }
 
@@ -717,6 +722,8 @@ int launch_decode(const DecodeArgs& a, cudaStream_t stream) {
   p.seq_lens = a.sequence_lengths;
   p.out = a.out;
   p.hdr = static_cast<WorkspaceHeader*>(a.workspace);
+  p.wait_limit = wait_limit_cycles();
+  p.out_f32 = a.out_f32 ? 1 : 0;
   p.num_seqs = a.num_seqs;
   p.num_q_heads = a.num_q_heads;
   p.num_kv_heads = a.num_kv_heads;
@@ -742,8 +749,6 @@ int launch_decode(const DecodeArgs& a, cudaStream_t stream) {
   p.part_l = reinterpret_cast<float*>(ws + sizeof(WorkspaceHeader) + align256(rows * 4));
   p.part_acc = reinterpret_cast<float*>(ws + sizeof(WorkspaceHeader) + 2 * align256(rows * 4));
 
-  cudaError_t e = cudaMemsetAsync(a.workspace, 0, 8, stream);
-  if (e != cudaSuccess) return (int)e;
   const int sms = cached_sm_count();
   int rc;
   if (a.dtype == 0)
@@ -760,9 +765,22 @@ int launch_decode(const DecodeArgs& a, cudaStream_t stream) {
   if (rc != 0) return rc;
   if (split) {
     const long long out_rows = (long long)a.num_seqs * a.num_q_heads;
-    rc = launch_lse_combine(p.part_m, p.part_l, p.part_acc, a.out, a.m_out, a.l_out, a.acc_out, p.num_parts, out_rows,
-                            a.head_dim, a.dtype, 1, p.num_parts, a.head_dim, (long long)p.num_parts * a.head_dim,
-                            stream);
+    const PartialsView in{p.part_m, p.part_l, p.part_acc, 1, p.num_parts, a.head_dim, (long long)p.num_parts * a.head_dim};
+    TripleOut triple;
+    if (a.packed_out) {
+      // one row = head_dim values of acc, then m, then l
+      triple.acc = a.packed_out;
+      triple.m = a.packed_out + a.head_dim;
+      triple.l = a.packed_out + a.head_dim + 1;
+      triple.row_stride_ml = triple.row_stride_acc = a.head_dim + 2;
+    } else {
+      triple.m = a.m_out;
+      triple.l = a.l_out;
+      triple.acc = a.acc_out;
+      triple.row_stride_ml = 1;
+      triple.row_stride_acc = a.head_dim;
+    }
+    rc = launch_lse_combine(in, a.out, a.out_f32, triple, p.num_parts, out_rows, a.head_dim, a.dtype, stream);
   }
   return rc;
 }

@@ -255,18 +255,14 @@ int launch_fill(const FillArgs& a, cudaStream_t stream) {
     long long groups = (a.num_tokens + kGroupTokens - 1) / kGroupTokens * parts;
     const long long max_groups = 148LL * 32;
     if (groups > max_groups) groups = max_groups;
-    static bool configured[2][64] = {};
-    int dev = 0;
-    cudaGetDevice(&dev);
-    const int which = a.slot_mapping ? 1 : 0;
-    if (dev < 64 && !configured[which][dev]) {
-      cudaError_t e = which ? cudaFuncSetAttribute(fill_kv_pages_grouped_kernel<true>,
-                                                   cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024)
-                            : cudaFuncSetAttribute(fill_kv_pages_grouped_kernel<false>,
-                                                   cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
-      if (e != cudaSuccess) return (int)e;
-      configured[which][dev] = true;
-    }
+    static DeviceOnce configured;
+    const int rc = configured.run([] {
+      cudaError_t e = cudaFuncSetAttribute(fill_kv_pages_grouped_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
+      if (e == cudaSuccess)
+        e = cudaFuncSetAttribute(fill_kv_pages_grouped_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
+      return (int)e;
+    });
+    if (rc != 0) return rc;
     if (a.slot_mapping)
       fill_kv_pages_grouped_kernel<true><<<(unsigned)groups, 256, grouped_smem, stream>>>(
           (const uint4*)a.new_keys, (const uint4*)a.new_values, (uint16_t*)a.k_pool, (uint16_t*)a.v_pool,

@@ -9,7 +9,36 @@
 #include <stddef.h>
 #include <stdint.h>
 
+#include <atomic>
+#include <mutex>
+
 namespace pal {
+
+constexpr int kMaxDevices = 64;
+
+// One-time, per-device set-up (kernel attributes, device properties) that any host thread may trigger:
+// the first caller on a device runs `fn` under a lock, later callers see the flag and skip it.
+class DeviceOnce {
+ public:
+  // fn() returns a cudaError_t as int; a failure is returned and the set-up is retried by the next call.
+  template <typename F>
+  int run(F&& fn) {
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return (int)e;
+    if (dev < 0 || dev >= kMaxDevices) return fn();
+    if (done_[dev].load(std::memory_order_acquire)) return 0;
+    std::lock_guard<std::mutex> lock(mu_);
+    if (done_[dev].load(std::memory_order_relaxed)) return 0;
+    const int rc = fn();
+    if (rc == 0) done_[dev].store(true, std::memory_order_release);
+    return rc;
+  }
+
+ private:
+  std::mutex mu_;
+  std::atomic<bool> done_[kMaxDevices] = {};
+};
 
 struct FillArgs {
   const void* new_keys;
@@ -37,10 +66,12 @@ struct DecodeArgs {
   const void* new_values = nullptr;
   const uint32_t* page_table;
   const int32_t* sequence_lengths;
-  void* out;            // [S, Hq, D] in the query dtype (null when only the triple is wanted)
+  void* out;            // [S, Hq, D] in the query dtype or float32 (null when only the triple is wanted)
+  bool out_f32 = false;
   float* m_out;         // optional un-normalised triple [S, Hq], [S, Hq], [S, Hq, D]
   float* l_out;
   float* acc_out;
+  float* packed_out = nullptr;  // or the same triple as one [S*Hq, D + 2] buffer: acc, then m, then l
   int num_seqs;
   int num_q_heads;
   int num_kv_heads;
@@ -66,6 +97,7 @@ struct PrefillArgs {
   const int32_t* cu_seqlens = nullptr;  // ragged form: [S + 1] row offsets; tokens_per_seq is then the longest sequence
   long long total_tokens = 0;           // ragged form: rows of q_prompt / k_prompt / v_prompt
   void* out;
+  bool out_f32 = false;
   int num_seqs;
   int tokens_per_seq;
   int num_q_heads;
@@ -85,10 +117,24 @@ struct PrefillArgs {
 // leaves a message via set_error() on failure.
 int launch_fill(const FillArgs& a, cudaStream_t stream);
 int launch_decode(const DecodeArgs& a, cudaStream_t stream);
-int launch_lse_combine(const float* m, const float* l, const float* acc, void* out, float* m_out, float* l_out,
-                       float* acc_out, int num_parts, long long rows, int head_dim, int dtype, long long part_stride_ml,
-                       long long row_stride_ml, long long part_stride_acc, long long row_stride_acc,
-                       cudaStream_t stream);
+// Strided views of a set of partial triples (element strides): partition j of row r has its m / l at
+// m[j * part_stride_ml + r * row_stride_ml] and its acc row at acc + j * part_stride_acc + r * row_stride_acc.
+struct PartialsView {
+  const float* m;
+  const float* l;
+  const float* acc;
+  long long part_stride_ml, row_stride_ml, part_stride_acc, row_stride_acc;
+};
+// Where a merged, still un-normalised triple goes (all optional): row r's acc at acc + r * row_stride_acc, its m / l at
+// m[r * row_stride_ml].
+struct TripleOut {
+  float* m = nullptr;
+  float* l = nullptr;
+  float* acc = nullptr;
+  long long row_stride_ml = 1, row_stride_acc = 0;
+};
+int launch_lse_combine(const PartialsView& in, void* out, bool out_f32, const TripleOut& triple, int num_parts,
+                       long long rows, int head_dim, int dtype, cudaStream_t stream);
 int launch_prefill_mma(const PrefillArgs& a, cudaStream_t stream);
 int launch_prefill_tcgen05(const PrefillArgs& a, cudaStream_t stream);
 
@@ -98,5 +144,11 @@ int decode_num_partitions(int max_pages_per_seq, int partition_pages);
 int decode_auto_partition_pages(int num_seqs, int num_q_heads, int num_kv_heads, int max_pages_per_seq);
 
 void set_error(const char* fmt, ...);
+// cudaError_t (as int) or negative PAL_ERR_* -> PAL_* return code, with the message set
+int cuda_rc(int rc, const char* what);
+
+// Limit, in SM clock cycles, of every bounded device-side wait of the launches that follow (process-wide).
+long long wait_limit_cycles();
+int cached_sm_count();
 
 }  // namespace pal

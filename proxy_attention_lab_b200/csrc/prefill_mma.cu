@@ -33,6 +33,7 @@ struct PrefillParams {
   const int32_t* hist_lens;
   const int32_t* cu_seqlens;  // ragged batches: first row of each sequence in q / k_new / v_new / out; null = uniform n_new
   void* out;
+  int out_f32;  // out holds float32 instead of the input type
   int num_seqs, n_new, num_q_heads, num_kv_heads, group, max_pages_per_seq;
   long long num_pages;
   float scale_log2;
@@ -279,10 +280,16 @@ __global__ void __launch_bounds__(kPrefillThreads) prefill_mma_kernel(const Pref
     const int qi = rr ? i_hi : i_lo;
     if (qi >= N) continue;
     const float inv = l_run[rr] > 0.f ? 1.f / l_run[rr] : 0.f;
-    uint32_t* orow = reinterpret_cast<uint32_t*>(outp + ((row0 + qi) * p.num_q_heads + h) * D);
+    const size_t off = ((row0 + qi) * p.num_q_heads + h) * D;
+    if (p.out_f32) {
+      float2* orow = reinterpret_cast<float2*>(static_cast<float*>(p.out) + off);
 #pragma unroll
-    for (int nd = 0; nd < NDT; ++nd)
-      orow[nd * 4 + t] = MMA::pack(o[nd][2 * rr] * inv, o[nd][2 * rr + 1] * inv);
+      for (int nd = 0; nd < NDT; ++nd) orow[nd * 4 + t] = make_float2(o[nd][2 * rr] * inv, o[nd][2 * rr + 1] * inv);
+    } else {
+      uint32_t* orow = reinterpret_cast<uint32_t*>(outp + off);
+#pragma unroll
+      for (int nd = 0; nd < NDT; ++nd) orow[nd * 4 + t] = MMA::pack(o[nd][2 * rr] * inv, o[nd][2 * rr + 1] * inv);
+    }
   }
 }
 
@@ -290,14 +297,9 @@ template <typename T, int D, int TPP>
 int launch_inst(const PrefillParams& p, cudaStream_t stream) {
   constexpr int smem = 3 * kBM * (D + 8) * 2;
   auto kern = prefill_mma_kernel<T, D, TPP>;
-  static bool configured[64] = {};
-  int dev = 0;
-  cudaGetDevice(&dev);
-  if (dev < 64 && !configured[dev]) {
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-    if (e != cudaSuccess) return (int)e;
-    configured[dev] = true;
-  }
+  static DeviceOnce configured;  // one per instantiation
+  const int rc = configured.run([&] { return (int)cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem); });
+  if (rc != 0) return rc;
   dim3 grid((p.n_new + kBM - 1) / kBM, p.num_q_heads, p.num_seqs);
   kern<<<grid, kPrefillThreads, smem, stream>>>(p);
   return (int)cudaGetLastError();
@@ -338,6 +340,7 @@ int launch_prefill_mma(const PrefillArgs& a, cudaStream_t stream) {
   p.hist_lens = a.history_lens;
   p.cu_seqlens = a.cu_seqlens;
   p.out = a.out;
+  p.out_f32 = a.out_f32 ? 1 : 0;
   p.num_seqs = a.num_seqs;
   p.n_new = a.tokens_per_seq;
   p.num_q_heads = a.num_q_heads;

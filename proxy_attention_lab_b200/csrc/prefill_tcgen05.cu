@@ -67,7 +67,8 @@ struct TcParams {
   const int32_t* hist_lens;
   const int32_t* cu_seqlens;  // ragged batches: first row of each sequence; null = every sequence has n_new rows
   void* out;
-  unsigned int* status;
+  WaitCtx status;
+  int out_f32;  // out holds float32 instead of the input type (stored row by row, not through the TMA path)
   int num_seqs, n_new, num_q_heads, num_kv_heads, group, max_pages_per_seq;
   long long num_pages;
   float scale_log2;
@@ -491,7 +492,10 @@ __global__ void __launch_bounds__(64 + 128 * NQ, 1)
         v_dense[st] = make_desc(sV_u + st * kTileBytes, kHalfTileBytes, 1024, kLayoutSw128);
         v_hist[st] = make_desc(sV_u + st * kTileBytes, 16, 256, kLayoutSw32);
       }
-      bool ok = mbar_wait(q_full, 0, p.status);
+      // Every lane waits (each needs to observe the barrier itself), and the outcomes are combined so that the warp
+      // leaves together if a wait expires: elect.sync below names all 32 lanes.
+      auto wait_all = [&](uint64_t* bar, uint32_t parity) { return __all_sync(0xffffffffu, mbar_wait(bar, parity, p.status)) != 0; };
+      bool ok = wait_all(q_full, 0);
 
       // S_q(j) = Q_q . K(j)^T into TMEM columns [128 q, 128 q + 128)
       auto issue_qk = [&](int q, int j) {
@@ -541,7 +545,7 @@ __global__ void __launch_bounds__(64 + 128 * NQ, 1)
         tc_commit(&o_done[q]);
       };
 
-      if (ok) ok = mbar_wait(&k_full[0], 0, p.status);
+      if (ok) ok = wait_all(&k_full[0], 0);
       if (ok) {
         tc_fence_after();
         for (int q = 0; q < NQ; ++q) issue_qk(q, 0);
@@ -549,15 +553,15 @@ __global__ void __launch_bounds__(64 + 128 * NQ, 1)
       }
       for (int j = 0; j < num_tiles && ok; ++j) {
         const int st = j & 1;
-        ok = mbar_wait(&v_full[st], (j >> 1) & 1, p.status);
+        ok = wait_all(&v_full[st], (j >> 1) & 1);
         for (int q = 0; q < NQ && ok; ++q) {
-          ok = mbar_wait(&p_full[q], j & 1, p.status);
+          ok = wait_all(&p_full[q], j & 1);
           if (!ok) break;
           tc_fence_after();
           issue_pv(q, j);
           if (j + 1 < num_tiles) {
             if (q == 0) {
-              ok = mbar_wait(&k_full[(j + 1) & 1], ((j + 1) >> 1) & 1, p.status);
+              ok = wait_all(&k_full[(j + 1) & 1], ((j + 1) >> 1) & 1);
               if (!ok) break;
               tc_fence_after();
             }
@@ -656,6 +660,20 @@ __global__ void __launch_bounds__(64 + 128 * NQ, 1)
         }
         fence_proxy_async_smem();
       }
+      // In a ragged batch the dense tile that holds a sequence's last new tokens also holds rows of the next sequence.
+      // Their keys are masked, but their V rows would still be multiplied by P = 0: zero them (0 * NaN again).
+      if (q == 0 && !paged && p.cu_seqlens != nullptr && (jd + 1) * kTile > N) {
+        if (!(ok = mbar_wait(&v_full[j & 1], (j >> 1) & 1, p.status))) break;
+        if (jd * kTile + row >= N) {
+          // dense V tile: [2 blocks of 64 head-dim elements][128 tokens][128 bytes]; the swizzle permutes within a row
+          unsigned char* vt = sV + (j & 1) * kTileBytes + row * 128;
+#pragma unroll
+          for (int nb = 0; nb < 2; ++nb)
+#pragma unroll
+            for (int c = 0; c < 8; ++c) *reinterpret_cast<uint4*>(vt + nb * kHalfTileBytes + c * 16) = make_uint4(0u, 0u, 0u, 0u);
+        }
+        fence_proxy_async_smem();
+      }
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&p_full[q]);
@@ -667,17 +685,28 @@ __global__ void __launch_bounds__(64 + 128 * NQ, 1)
     // shared memory: the head's Q tile is no longer read by any MMA, has exactly the size and swizzled layout of the
     // output tile, and two TMA stores write it out in whole lines.  A partial tile of a ragged batch would run into the
     // next sequence's rows, so it is stored row by row from registers.
-    const bool tma_out = p.cu_seqlens == nullptr || t0q + kTile <= N;
+    const bool tma_out = !p.out_f32 && (p.cu_seqlens == nullptr || t0q + kTile <= N);
     if (ok) {
       tc_fence_after();
       const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
-      T* orow = static_cast<T*>(p.out) + ((out_row0 + qi) * p.num_q_heads + h0 + q * kHeadStep) * kD;
+      const size_t out_off = ((out_row0 + qi) * p.num_q_heads + h0 + q * kHeadStep) * kD;
+      T* orow = static_cast<T*>(p.out) + out_off;
       unsigned char* stage = sQ + q * kTileBytes + row * 128;
 #pragma unroll
       for (int c4 = 0; c4 < 4; ++c4) {
         uint32_t v[32];
         tmem_ld32(tO + c4 * 32, v);
         tmem_wait_ld();
+        if (p.out_f32) {
+          if (qi < N) {
+            float4* o32 = reinterpret_cast<float4*>(static_cast<float*>(p.out) + out_off + c4 * 32);
+#pragma unroll
+            for (int i = 0; i < 8; ++i)
+              o32[i] = make_float4(__uint_as_float(v[4 * i]) * inv, __uint_as_float(v[4 * i + 1]) * inv,
+                                   __uint_as_float(v[4 * i + 2]) * inv, __uint_as_float(v[4 * i + 3]) * inv);
+          }
+          continue;
+        }
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
           uint4 w;
@@ -719,16 +748,15 @@ __global__ void __launch_bounds__(64 + 128 * NQ, 1)
 
 // ---- host side -------------------------------------------------------------------------------
 PFN_cuTensorMapEncodeTiled_v12000 get_encode_fn() {
-  static PFN_cuTensorMapEncodeTiled_v12000 fn = nullptr;
-  static bool tried = false;
-  if (!tried) {
-    tried = true;
+  // resolved once; the initialisation of a function-local static is safe against concurrent first calls
+  static const PFN_cuTensorMapEncodeTiled_v12000 fn = [] {
     void* ptr = nullptr;
     cudaDriverEntryPointQueryResult qres;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) == cudaSuccess &&
-        qres == cudaDriverEntryPointSuccess)
-      fn = reinterpret_cast<PFN_cuTensorMapEncodeTiled_v12000>(ptr);
-  }
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) != cudaSuccess ||
+        qres != cudaDriverEntryPointSuccess)
+      ptr = nullptr;
+    return reinterpret_cast<PFN_cuTensorMapEncodeTiled_v12000>(ptr);
+  }();
   return fn;
 }
 
@@ -754,14 +782,10 @@ template <typename T, int NQ, bool PAIR_TILES>
 int launch_tc(const TcParams& p, const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv,
               const CUtensorMap& mvp, const CUtensorMap& mo, cudaStream_t stream) {
   auto kern = prefill_tcgen05_kernel<T, NQ, PAIR_TILES>;
-  static bool configured[64] = {};
-  int dev = 0;
-  cudaGetDevice(&dev);
-  if (dev < 64 && !configured[dev]) {
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, TcSmem<NQ>::kTotal);
-    if (e != cudaSuccess) return (int)e;
-    configured[dev] = true;
-  }
+  static DeviceOnce configured;  // one per instantiation
+  const int rc = configured.run(
+      [&] { return (int)cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, TcSmem<NQ>::kTotal); });
+  if (rc != 0) return rc;
   const int num_qt = (p.n_new + kTile - 1) / kTile;
   dim3 grid(PAIR_TILES ? (num_qt + 1) / 2 : num_qt, PAIR_TILES ? p.num_q_heads : p.num_q_heads / NQ, p.num_seqs);
   kern<<<grid, 64 + 128 * NQ, TcSmem<NQ>::kTotal, stream>>>(p, mq, mk, mv, mvp, mo);
@@ -789,7 +813,8 @@ int launch_prefill_tcgen05(const PrefillArgs& a, cudaStream_t stream) {
   p.hist_lens = a.history_lens;
   p.cu_seqlens = a.cu_seqlens;
   p.out = a.out;
-  p.status = &static_cast<WorkspaceHeader*>(a.workspace)->status;
+  p.status = WaitCtx{&static_cast<WorkspaceHeader*>(a.workspace)->status, wait_limit_cycles()};
+  p.out_f32 = a.out_f32 ? 1 : 0;
   p.num_seqs = a.num_seqs;
   p.n_new = a.tokens_per_seq;
   p.num_q_heads = a.num_q_heads;
@@ -825,8 +850,6 @@ int launch_prefill_tcgen05(const PrefillArgs& a, cudaStream_t stream) {
   } else {
     mvp = mv;  // never dereferenced: without pages every history length is treated as 0
   }
-  cudaError_t e = cudaMemsetAsync(a.workspace, 0, 8, stream);
-  if (e != cudaSuccess) return (int)e;
   // Heads that share a kv head go two to a CTA; otherwise (odd group sizes, e.g. one query head per kv head) two query
   // tiles of one head do, and only a sequence of a single query tile leaves a CTA with one accumulator tile.
   const bool pair_heads = (p.group % 2) == 0;

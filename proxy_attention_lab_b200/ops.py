@@ -2,16 +2,19 @@
 
 Same names, argument order and cache layouts as the reference's Python layer
 (``src/proxy_attention_lab/ops.py:33-171``, bound in ``src/pal_core/bindings.cpp:44-222``),
-with ``torch.Tensor`` where the reference takes ``mx.array`` and eager launches on the current
-CUDA stream where the reference builds lazy MLX graph nodes.  Every operator launches
-hand-written sm_100a kernels through the C ABI; nothing here computes on the host and there is
-no fallback path.
+with ``torch.Tensor`` where the reference takes ``mx.array`` and eager launches on a CUDA stream
+where the reference builds lazy MLX graph nodes.  Every operator launches hand-written sm_100a
+kernels through the C ABI; nothing here computes on the host and there is no fallback path.
+
+Streams: ``stream=None`` means torch's current stream.  When a stream is named (a
+``torch.cuda.Stream`` or a raw ``cudaStream_t`` integer) the whole operator - index conversions,
+contiguity copies, output and workspace allocation, and the launch - runs with that stream current,
+so everything the kernel reads is ordered before it and the outputs belong to that stream.
 """
 
 from __future__ import annotations
 
 import functools
-import math
 
 import torch
 
@@ -28,14 +31,14 @@ def _dtype_code(dtype: torch.dtype) -> int:
         raise ValueError(f"dtype {dtype} is not supported (float16 and bfloat16 are)") from None
 
 
-def _stream_ptr(stream, device) -> int:
-    if stream is None:
-        return torch.cuda.current_stream(device).cuda_stream
-    if isinstance(stream, torch.cuda.Stream):
-        return stream.cuda_stream
-    if isinstance(stream, int):
-        return stream
-    raise TypeError("stream must be None, a torch.cuda.Stream or a raw cudaStream_t integer")
+def _out_code(in_dtype: torch.dtype, out_dtype) -> tuple:
+    """(dtype argument of the C call, torch dtype of the output): the input type, or float32 on request."""
+    code = _dtype_code(in_dtype)
+    if out_dtype is None or out_dtype == in_dtype:
+        return code, in_dtype
+    if out_dtype == torch.float32:
+        return code | _lib.PAL_OUT_F32, torch.float32
+    raise ValueError(f"out_dtype must be None, the input dtype ({in_dtype}) or torch.float32, got {out_dtype}")
 
 
 def _need_cuda(name: str, t: torch.Tensor) -> None:
@@ -62,40 +65,75 @@ def _ptr(t) -> int:
     return 0 if t is None or t.numel() == 0 else t.data_ptr()
 
 
+class _Scope:
+    """Makes ``device`` current and, when the caller named a stream, makes that stream torch's current one for the
+    duration of an operator; yields the raw ``cudaStream_t``.  Costs two cheap queries when nothing has to change."""
+
+    __slots__ = ("device", "stream", "_guards")
+
+    def __init__(self, device, stream):
+        if stream is not None and not isinstance(stream, (torch.cuda.Stream, int)):
+            raise TypeError("stream must be None, a torch.cuda.Stream or a raw cudaStream_t integer")
+        self.device, self.stream, self._guards = device, stream, None
+
+    def __enter__(self) -> int:
+        dev, stream = self.device, self.stream
+        guards = []
+        if torch.cuda.current_device() != dev.index:
+            g = torch.cuda.device(dev)
+            g.__enter__()
+            guards.append(g)
+        if stream is not None:
+            if isinstance(stream, int):
+                stream = torch.cuda.ExternalStream(stream, device=dev)
+            if stream.cuda_stream != torch.cuda.current_stream(dev).cuda_stream:
+                g = torch.cuda.stream(stream)
+                g.__enter__()
+                guards.append(g)
+        self._guards = guards
+        return torch.cuda.current_stream(dev).cuda_stream
+
+    def __exit__(self, *exc):
+        for g in reversed(self._guards):
+            g.__exit__(*exc)
+        return False
+
+
+# (device index, stream) -> every scratch buffer ever handed out for that pair, newest (largest) last
 _WORKSPACES: dict = {}
 
 
 def _workspace(nbytes: int, device, stream_ptr: int) -> torch.Tensor:
-    """Scratch for one call.  Calls on one stream run in order, so they share one buffer per (device, stream);
-    it only ever grows, which also keeps its address stable for a caller that captures the call in a CUDA graph."""
+    """Scratch for one call, allocated (zeroed, as the C ABI asks for the header) on the stream that will use it.
+
+    Calls on one stream run in order, so they share one buffer per (device, stream).  When a call needs more than the
+    newest buffer holds, a larger one (at least twice the size) is added; the earlier buffers are kept for the life of
+    the process, because a CUDA graph captured from an earlier call still writes to the address it recorded.
+    """
     need = max(int(nbytes), 256)
     key = (device.index, stream_ptr)
-    ws = _WORKSPACES.get(key)
-    if ws is None or ws.numel() < need:
-        ws = torch.empty(max(need, 4096), dtype=torch.uint8, device=device)
-        _WORKSPACES[key] = ws
-    return ws
-
-
-class _NoGuard:
-    def __enter__(self):
-        return None
-
-    def __exit__(self, *exc):
-        return False
-
-
-_NO_GUARD = _NoGuard()
-
-
-def _on(device):
-    """Device guard that costs nothing when `device` is already current."""
-    return _NO_GUARD if torch.cuda.current_device() == device.index else torch.cuda.device(device)
+    held = _WORKSPACES.get(key)
+    if held is None:
+        held = _WORKSPACES[key] = []
+    if not held or held[-1].numel() < need:
+        held.append(torch.zeros(max(need, 2 * held[-1].numel() if held else 4096), dtype=torch.uint8, device=device))
+    return held[-1]
 
 
 @functools.lru_cache(maxsize=256)
 def _decode_ws_bytes(S, hq, hkv, d, tpp, mp, pp) -> int:
     return lib.pal_decode_workspace_bytes(S, hq, hkv, d, tpp, mp, pp)
+
+
+def check_status(stream=None, device=None) -> None:
+    """Raise ``RuntimeError`` if a kernel of the last call on this (device, stream) gave up a bounded wait.
+
+    Synchronises with the stream; meant for tests and debugging."""
+    device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    with _Scope(device, stream) as sp:
+        held = _WORKSPACES.get((device.index, sp))
+        if held:
+            _lib.check(lib.pal_check_status(held[-1].data_ptr(), sp))
 
 
 # ---------------------------------------------------------------------------------------------
@@ -168,38 +206,39 @@ def fill_kv_pages(
         raise ValueError(f"new_keys / new_values must be [T, {hkv}, {d}], got {tuple(new_keys.shape)} / {tuple(new_values.shape)}")
     if tuple(global_key_pool.shape) != (num_pages, hkv, d // 8, tpp, 8):
         raise ValueError("global_key_pool shape does not match global_value_pool")
-    if not inplace:
-        global_key_pool = global_key_pool.clone()
-        global_value_pool = global_value_pool.clone()
-    if not (global_key_pool.is_contiguous() and global_value_pool.is_contiguous()):
-        raise ValueError("the page pools must be contiguous")
     T = new_keys.shape[0]
-    if T == 0:
-        return global_key_pool, global_value_pool
-    new_keys, new_values = _contig(new_keys), _contig(new_values)
+    if slot_mapping is not None:
+        _need_cuda("slot_mapping", slot_mapping)
+        if slot_mapping.numel() != T:
+            raise ValueError("slot_mapping must have one entry per new token")
+    else:
+        if page_table is None or current_token_write_positions is None or query_to_seq_map is None:
+            raise ValueError("page_table, current_token_write_positions and query_to_seq_map are required")
+        for name, t in (("page_table", page_table), ("current_token_write_positions", current_token_write_positions),
+                        ("query_to_seq_map", query_to_seq_map)):
+            _need_cuda(name, t)
+        if page_table.dim() != 2:
+            raise ValueError("page_table must be 2-D [num_sequences, max_logical_pages]")
+        if current_token_write_positions.numel() != T or query_to_seq_map.numel() != T:
+            raise ValueError("write positions and query_to_seq_map must have one entry per new token")
     dev = global_value_pool.device
-    with _on(dev):
-        sp = _stream_ptr(stream, dev)
+    with _Scope(dev, stream) as sp:
+        if not inplace:
+            global_key_pool = global_key_pool.clone()
+            global_value_pool = global_value_pool.clone()
+        if not (global_key_pool.is_contiguous() and global_value_pool.is_contiguous()):
+            raise ValueError("the page pools must be contiguous")
+        if T == 0:
+            return global_key_pool, global_value_pool
+        new_keys, new_values = _contig(new_keys), _contig(new_values)
         if slot_mapping is not None:
-            _need_cuda("slot_mapping", slot_mapping)
             slots = _contig(slot_mapping.to(torch.int64))
-            if slots.numel() != T:
-                raise ValueError("slot_mapping must have one entry per new token")
             rc = lib.pal_fill_kv_pages_slots(new_keys.data_ptr(), new_values.data_ptr(), global_key_pool.data_ptr(),
                                              global_value_pool.data_ptr(), slots.data_ptr(), T, hkv, d, tpp, num_pages, dt, sp)
         else:
-            if page_table is None or current_token_write_positions is None or query_to_seq_map is None:
-                raise ValueError("page_table, current_token_write_positions and query_to_seq_map are required")
-            for name, t in (("page_table", page_table), ("current_token_write_positions", current_token_write_positions),
-                            ("query_to_seq_map", query_to_seq_map)):
-                _need_cuda(name, t)
-            if page_table.dim() != 2:
-                raise ValueError("page_table must be 2-D [num_sequences, max_logical_pages]")
             pt = _index32("page_table", page_table)
             pos = _index32("current_token_write_positions", current_token_write_positions)
             seqmap = _index32("query_to_seq_map", query_to_seq_map)
-            if pos.numel() != T or seqmap.numel() != T:
-                raise ValueError("write positions and query_to_seq_map must have one entry per new token")
             rc = lib.pal_fill_kv_pages(new_keys.data_ptr(), new_values.data_ptr(), global_key_pool.data_ptr(),
                                        global_value_pool.data_ptr(), pt.data_ptr(), pos.data_ptr(), seqmap.data_ptr(), T,
                                        pt.shape[0], hkv, d, tpp, num_pages, pt.shape[1], dt, sp)
@@ -225,12 +264,21 @@ def _decode_shapes(queries, k_cache_pool, v_cache_pool, page_table, sequence_len
         raise ValueError("queries and both pools must share one dtype")
     if page_table.dim() != 2:
         raise ValueError("page_table must be 2-D [num_sequences, max_logical_pages]")
-    hq = queries.shape[1] if queries.dim() == 3 else 1  # ops.cpp:62-66
-    if queries.shape[-1] != d and queries.dim() >= 2:
-        raise ValueError(f"queries head_dim {queries.shape[-1]} does not match the cache head_dim {d}")
     S = page_table.shape[0]
-    if queries.dim() >= 2 and queries.shape[0] < S:
-        raise ValueError("queries has fewer rows than page_table has sequences")
+    # ops.cpp:62-66: the head count comes from a 3-D query only; the kernel then reads row s of the flat buffer as
+    # Hq * D elements (paged_attention_decode.h.metal:106-108), whatever the number of dimensions.
+    hq = queries.shape[1] if queries.dim() == 3 else 1
+    if queries.dim() in (2, 3):
+        if queries.shape[-1] != d:
+            raise ValueError(f"queries head_dim {queries.shape[-1]} does not match the cache head_dim {d}")
+        if queries.shape[0] < S:
+            raise ValueError("queries has fewer rows than page_table has sequences")
+    elif queries.dim() == 1:
+        # a flat buffer of S rows of head_dim elements, one query head
+        if queries.numel() < S * d or queries.numel() % d != 0:
+            raise ValueError(f"1-D queries must hold a whole number (>= {S}) of rows of head_dim = {d} elements, got {queries.numel()} elements")
+    else:
+        raise ValueError("queries must be 1-D, 2-D [S, D] or 3-D [S, Hq, D]")
     if sequence_lengths.numel() < S:
         raise ValueError("sequence_lengths has fewer entries than page_table has sequences")
     if hq % hkv != 0:
@@ -239,36 +287,36 @@ def _decode_shapes(queries, k_cache_pool, v_cache_pool, page_table, sequence_len
 
 
 def paged_attention_decode(queries, k_cache_pool, v_cache_pool, page_table, sequence_lengths, *, stream=None,
-                           partition_pages=None, scale=None):
+                           partition_pages=None, scale=None, out_dtype=None):
     """One query token per sequence attending to its paged KV history.
 
-    ``queries [>=S, Hq, D]`` (2-D means one query head), pools in the reference layouts,
-    ``page_table [S, max_pages]``, ``sequence_lengths [S]``.  Returns ``[S, Hq, D]`` in the query
-    dtype.  ``partition_pages``: None = let the library choose, 0 = fused single pass,
-    n > 0 = two-pass split-KV with n-page partitions and a log-sum-exp combine.
+    ``queries [>=S, Hq, D]`` (2-D ``[>=S, D]`` or a flat 1-D buffer of such rows means one query head), pools in the
+    reference layouts, ``page_table [S, max_pages]``, ``sequence_lengths [S]``.  Returns ``[S, Hq, D]`` in the query
+    dtype, or in float32 with ``out_dtype=torch.float32`` (same arithmetic, the final rounding to 16 bits left out).
+    ``partition_pages``: None = let the library choose, 0 = fused single pass, n > 0 = two-pass split-KV with n-page
+    partitions and a log-sum-exp combine.
     """
     S, hq, hkv, d, tpp, num_pages = _decode_shapes(queries, k_cache_pool, v_cache_pool, page_table, sequence_lengths)
     dev = queries.device
-    out = torch.empty((S, hq, d), dtype=queries.dtype, device=dev)
-    if S == 0:
-        return out
-    q = _contig(queries)
-    pt = _index32("page_table", page_table)
-    lens = _index32("sequence_lengths", sequence_lengths)
+    code, odt = _out_code(queries.dtype, out_dtype)
     pp = _lib.PAL_DECODE_AUTO if partition_pages is None else int(partition_pages)
-    with _on(dev):
-        sp = _stream_ptr(stream, dev)
+    with _Scope(dev, stream) as sp:
+        out = torch.empty((S, hq, d), dtype=odt, device=dev)
+        if S == 0:
+            return out
+        q = _contig(queries)
+        pt = _index32("page_table", page_table)
+        lens = _index32("sequence_lengths", sequence_lengths)
         ws = _workspace(_decode_ws_bytes(S, hq, hkv, d, tpp, pt.shape[1], pp), dev, sp)
         rc = lib.pal_paged_attention_decode(q.data_ptr(), _ptr(k_cache_pool), _ptr(v_cache_pool), _ptr(pt), lens.data_ptr(),
                                             out.data_ptr(), S, hq, hkv, d, tpp, num_pages, pt.shape[1],
-                                            0.0 if scale is None else float(scale), _dtype_code(q.dtype), pp,
-                                            ws.data_ptr(), ws.numel(), sp)
+                                            0.0 if scale is None else float(scale), code, pp, ws.data_ptr(), ws.numel(), sp)
         _lib.check(rc)
     return out
 
 
 def paged_attention_decode_append(new_keys, new_values, queries, k_cache_pool, v_cache_pool, page_table, sequence_lengths, *,
-                                  stream=None, partition_pages=None, scale=None):
+                                  stream=None, partition_pages=None, scale=None, out_dtype=None):
     """``fill_kv_pages`` of each sequence's newest token and ``paged_attention_decode`` in one launch.
 
     ``new_keys / new_values [S, Hkv, D]`` belong to position ``sequence_lengths[s] - 1`` (the lengths already
@@ -281,52 +329,64 @@ def paged_attention_decode_append(new_keys, new_values, queries, k_cache_pool, v
         if tuple(t.shape) != (S, hkv, d) or t.dtype != queries.dtype:
             raise ValueError(f"{name} must be [{S}, {hkv}, {d}] of {queries.dtype}")
     dev = queries.device
-    out = torch.empty((S, hq, d), dtype=queries.dtype, device=dev)
-    if S == 0:
-        return out
-    q = _contig(queries)
-    nk, nv = _contig(new_keys), _contig(new_values)
-    pt = _index32("page_table", page_table)
-    lens = _index32("sequence_lengths", sequence_lengths)
+    code, odt = _out_code(queries.dtype, out_dtype)
     pp = _lib.PAL_DECODE_AUTO if partition_pages is None else int(partition_pages)
-    with _on(dev):
-        sp = _stream_ptr(stream, dev)
+    with _Scope(dev, stream) as sp:
+        out = torch.empty((S, hq, d), dtype=odt, device=dev)
+        if S == 0:
+            return out
+        q = _contig(queries)
+        nk, nv = _contig(new_keys), _contig(new_values)
+        pt = _index32("page_table", page_table)
+        lens = _index32("sequence_lengths", sequence_lengths)
         ws = _workspace(_decode_ws_bytes(S, hq, hkv, d, tpp, pt.shape[1], pp), dev, sp)
         rc = lib.pal_paged_attention_decode_append(nk.data_ptr(), nv.data_ptr(), q.data_ptr(), _ptr(k_cache_pool),
                                                    _ptr(v_cache_pool), _ptr(pt), lens.data_ptr(), out.data_ptr(), S, hq, hkv, d,
                                                    tpp, num_pages, pt.shape[1], 0.0 if scale is None else float(scale),
-                                                   _dtype_code(q.dtype), pp, ws.data_ptr(), ws.numel(), sp)
+                                                   code, pp, ws.data_ptr(), ws.numel(), sp)
         _lib.check(rc)
     return out
 
 
 def paged_attention_decode_partials(queries, k_cache_pool, v_cache_pool, page_table, sequence_lengths, *,
-                                    partition_pages: int = 256, scale=None, stream=None):
+                                    partition_pages: int = 256, scale=None, stream=None, packed: bool = False, out=None):
     """Split-KV pass without the final normalisation: returns fp32 ``(m [S,Hq], l [S,Hq], acc [S,Hq,D])``.
 
     For callers that merge partial results themselves, e.g. GPUs that each hold a slice of every
-    sequence's context; merge with :func:`lse_combine`.
+    sequence's context; merge with :func:`lse_combine`.  ``packed=True`` returns the same triple as one
+    ``[S*Hq, D + 2]`` buffer (``acc``, then ``m``, then ``l`` in every row; written into ``out`` when given) - the
+    form a single collective moves; merge gathered buffers with :func:`lse_combine_packed`.
     """
     S, hq, hkv, d, tpp, num_pages = _decode_shapes(queries, k_cache_pool, v_cache_pool, page_table, sequence_lengths)
     dev = queries.device
-    m = torch.empty((S, hq), dtype=torch.float32, device=dev)
-    l = torch.empty((S, hq), dtype=torch.float32, device=dev)
-    acc = torch.empty((S, hq, d), dtype=torch.float32, device=dev)
-    if S == 0:
-        return m, l, acc
-    q = _contig(queries)
-    pt = _index32("page_table", page_table)
-    lens = _index32("sequence_lengths", sequence_lengths)
-    with _on(dev):
-        sp = _stream_ptr(stream, dev)
+    with _Scope(dev, stream) as sp:
+        if packed:
+            if out is None:
+                out = torch.empty((S * hq, d + 2), dtype=torch.float32, device=dev)
+            elif out.dtype != torch.float32 or tuple(out.shape) != (S * hq, d + 2) or not out.is_contiguous() or out.device != dev:
+                raise ValueError(f"out must be a contiguous float32 [{S * hq}, {d + 2}] tensor on {dev}")
+            result = out
+        else:
+            m = torch.empty((S, hq), dtype=torch.float32, device=dev)
+            l = torch.empty((S, hq), dtype=torch.float32, device=dev)
+            acc = torch.empty((S, hq, d), dtype=torch.float32, device=dev)
+            result = (m, l, acc)
+        if S == 0:
+            return result
+        q = _contig(queries)
+        pt = _index32("page_table", page_table)
+        lens = _index32("sequence_lengths", sequence_lengths)
         ws = _workspace(_decode_ws_bytes(S, hq, hkv, d, tpp, pt.shape[1], int(partition_pages)), dev, sp)
-        rc = lib.pal_paged_attention_decode_partials(q.data_ptr(), _ptr(k_cache_pool), _ptr(v_cache_pool), _ptr(pt),
-                                                     lens.data_ptr(), m.data_ptr(), l.data_ptr(), acc.data_ptr(), S, hq, hkv, d,
-                                                     tpp, num_pages, pt.shape[1], 0.0 if scale is None else float(scale),
-                                                     _dtype_code(q.dtype), int(partition_pages), ws.data_ptr(), ws.numel(),
-                                                     sp)
+        common = (S, hq, hkv, d, tpp, num_pages, pt.shape[1], 0.0 if scale is None else float(scale), _dtype_code(q.dtype),
+                  int(partition_pages), ws.data_ptr(), ws.numel(), sp)
+        if packed:
+            rc = lib.pal_paged_attention_decode_partials_packed(q.data_ptr(), _ptr(k_cache_pool), _ptr(v_cache_pool), _ptr(pt),
+                                                                lens.data_ptr(), out.data_ptr(), *common)
+        else:
+            rc = lib.pal_paged_attention_decode_partials(q.data_ptr(), _ptr(k_cache_pool), _ptr(v_cache_pool), _ptr(pt),
+                                                         lens.data_ptr(), m.data_ptr(), l.data_ptr(), acc.data_ptr(), *common)
         _lib.check(rc)
-    return m, l, acc
+    return result
 
 
 def lse_combine(m, l, acc, out_dtype=torch.bfloat16, *, stream=None):
@@ -340,13 +400,31 @@ def lse_combine(m, l, acc, out_dtype=torch.bfloat16, *, stream=None):
     if m.shape != l.shape or acc.shape[:-1] != m.shape:
         raise ValueError("m, l and acc shapes do not agree")
     rows = m[0].numel()
-    out = torch.empty(tuple(acc.shape[1:]), dtype=out_dtype, device=m.device)
-    if rows == 0:
-        return out
-    m, l, acc = _contig(m), _contig(l), _contig(acc)
-    with torch.cuda.device(m.device):
-        _lib.check(lib.pal_lse_combine(m.data_ptr(), l.data_ptr(), acc.data_ptr(), out.data_ptr(), parts, rows, d,
-                                       _dtype_code(out_dtype), _stream_ptr(stream, m.device)))
+    code = _lib.PAL_OUT_F32 if out_dtype == torch.float32 else _dtype_code(out_dtype)
+    with _Scope(m.device, stream) as sp:
+        out = torch.empty(tuple(acc.shape[1:]), dtype=out_dtype, device=m.device)
+        if rows == 0:
+            return out
+        m, l, acc = _contig(m), _contig(l), _contig(acc)
+        _lib.check(lib.pal_lse_combine(m.data_ptr(), l.data_ptr(), acc.data_ptr(), out.data_ptr(), parts, rows, d, code, sp))
+    return out
+
+
+def lse_combine_packed(packed, out_dtype=torch.bfloat16, *, out_shape=None, stream=None):
+    """Merge packed partial triples ``[parts, rows, D + 2]`` (see :func:`paged_attention_decode_partials`) -> ``[rows, D]``
+    (or ``out_shape``, e.g. ``(S, Hq, D)``), reading the gathered buffer in place."""
+    _need_cuda("packed", packed)
+    if packed.dtype != torch.float32 or packed.dim() != 3 or packed.shape[-1] < 3 or not packed.is_contiguous():
+        raise ValueError("packed must be a contiguous float32 [parts, rows, D + 2] tensor")
+    parts, rows, d = packed.shape[0], packed.shape[1], packed.shape[2] - 2
+    code = _lib.PAL_OUT_F32 if out_dtype == torch.float32 else _dtype_code(out_dtype)
+    with _Scope(packed.device, stream) as sp:
+        out = torch.empty((rows, d) if out_shape is None else tuple(out_shape), dtype=out_dtype, device=packed.device)
+        if out.numel() != rows * d:
+            raise ValueError("out_shape does not hold rows * D elements")
+        if rows == 0 or parts == 0:
+            return out.zero_()
+        _lib.check(lib.pal_lse_combine_packed(packed.data_ptr(), out.data_ptr(), parts, rows, d, code, sp))
     return out
 
 
@@ -356,15 +434,7 @@ def lse_combine(m, l, acc, out_dtype=torch.bfloat16, *, stream=None):
 PREFILL_IMPL = {"auto": 0, "mma": 1, "tcgen05": 2}
 
 
-def paged_attention_prefill(q_prompt, k_prompt, v_prompt, k_cache_paged, v_cache_paged, page_table, context_len_arr, *,
-                            stream=None, impl="auto", scale=None):
-    """Causal attention of N new tokens per sequence over their paged history plus themselves.
-
-    ``q_prompt [S*N, Hq, D]``, ``k_prompt / v_prompt [S*N, Hkv, D]`` (sequence-major), history in
-    the pools through ``page_table [S, max_pages]`` with ``context_len_arr [S]`` history lengths.
-    Returns ``[S*N*Hq, D]`` (row ``(s*N + i)*Hq + h``), as the reference does
-    (``src/pal_core/src/paged_attention_prefill_primitive.cpp:188-192``).
-    """
+def _prefill_shapes(q_prompt, k_prompt, v_prompt, k_cache_paged, v_cache_paged, page_table, context_len_arr):
     for name, t in (("q_prompt", q_prompt), ("k_prompt", k_prompt), ("v_prompt", v_prompt),
                     ("k_cache_paged", k_cache_paged), ("v_cache_paged", v_cache_paged), ("page_table", page_table),
                     ("context_len_arr", context_len_arr)):
@@ -382,29 +452,44 @@ def paged_attention_prefill(q_prompt, k_prompt, v_prompt, k_cache_paged, v_cache
     if page_table.dim() != 2:
         raise ValueError("page_table must be 2-D [num_sequences, max_logical_pages]")
     S = context_len_arr.numel()
-    if S == 0 or total % S != 0:
-        # every sequence carries the same number of new tokens (paged_attention_prefill_primitive.cpp:115-116)
-        raise ValueError("the number of prompt tokens must be a multiple of the number of sequences")
     if page_table.shape[0] < S:
         raise ValueError("page_table has fewer rows than there are sequences")
     if hq % hkv != 0:
         raise ValueError(f"num_q_heads ({hq}) must be a multiple of num_kv_heads ({hkv})")
-    n = total // S
-    dev = q_prompt.device
-    out = torch.empty((total * hq, d), dtype=q_prompt.dtype, device=dev)
-    if total == 0:
-        return out
-    q, k, v = _contig(q_prompt), _contig(k_prompt), _contig(v_prompt)
     if not (k_cache_paged.is_contiguous() and v_cache_paged.is_contiguous()):
         raise ValueError("the page pools must be contiguous")
-    pt = _index32("page_table", page_table)
-    ctx = _index32("context_len_arr", context_len_arr)
-    with _on(dev):
-        sp = _stream_ptr(stream, dev)
-        ws = _workspace(lib.pal_prefill_workspace_bytes(S, n, hq, hkv, d), dev, sp)
+    return S, total, hq, hkv, d, tpp, num_pages
+
+
+def paged_attention_prefill(q_prompt, k_prompt, v_prompt, k_cache_paged, v_cache_paged, page_table, context_len_arr, *,
+                            stream=None, impl="auto", scale=None, out_dtype=None):
+    """Causal attention of N new tokens per sequence over their paged history plus themselves.
+
+    ``q_prompt [S*N, Hq, D]``, ``k_prompt / v_prompt [S*N, Hkv, D]`` (sequence-major), history in
+    the pools through ``page_table [S, max_pages]`` with ``context_len_arr [S]`` history lengths.
+    Returns ``[S*N*Hq, D]`` (row ``(s*N + i)*Hq + h``), as the reference does
+    (``src/pal_core/src/paged_attention_prefill_primitive.cpp:188-192``), in the query dtype or, with
+    ``out_dtype=torch.float32``, in float32.
+    """
+    S, total, hq, hkv, d, tpp, num_pages = _prefill_shapes(q_prompt, k_prompt, v_prompt, k_cache_paged, v_cache_paged,
+                                                           page_table, context_len_arr)
+    if S == 0 or total % S != 0:
+        # every sequence carries the same number of new tokens (paged_attention_prefill_primitive.cpp:115-116)
+        raise ValueError("the number of prompt tokens must be a multiple of the number of sequences")
+    n = total // S
+    dev = q_prompt.device
+    code, odt = _out_code(q_prompt.dtype, out_dtype)
+    with _Scope(dev, stream) as sp:
+        out = torch.empty((total * hq, d), dtype=odt, device=dev)
+        if total == 0:
+            return out
+        q, k, v = _contig(q_prompt), _contig(k_prompt), _contig(v_prompt)
+        pt = _index32("page_table", page_table)
+        ctx = _index32("context_len_arr", context_len_arr)
+        ws = _workspace(256, dev, sp)
         rc = lib.pal_paged_attention_prefill(q.data_ptr(), k.data_ptr(), v.data_ptr(), _ptr(k_cache_paged), _ptr(v_cache_paged),
                                              _ptr(pt), ctx.data_ptr(), out.data_ptr(), S, n, hq, hkv, d, tpp, num_pages,
-                                             pt.shape[1], 0.0 if scale is None else float(scale), _dtype_code(q.dtype),
+                                             pt.shape[1], 0.0 if scale is None else float(scale), code,
                                              PREFILL_IMPL[impl] if isinstance(impl, str) else int(impl), ws.data_ptr(),
                                              ws.numel(), sp)
         _lib.check(rc)
@@ -412,7 +497,7 @@ def paged_attention_prefill(q_prompt, k_prompt, v_prompt, k_cache_paged, v_cache
 
 
 def paged_attention_prefill_ragged(q_prompt, k_prompt, v_prompt, k_cache_paged, v_cache_paged, page_table, context_len_arr,
-                                   cu_seqlens, *, max_new_tokens=None, stream=None, impl="auto", scale=None):
+                                   cu_seqlens, *, max_new_tokens=None, stream=None, impl="auto", scale=None, out_dtype=None):
     """``paged_attention_prefill`` for batches whose sequences bring different numbers of new tokens.
 
     ``cu_seqlens [S + 1]`` (int32, starting at 0) gives each sequence's first row in ``q_prompt [T, Hq, D]`` and
@@ -420,48 +505,28 @@ def paged_attention_prefill_ragged(q_prompt, k_prompt, v_prompt, k_cache_paged, 
     is a decode step, so prefill chunks and decode steps can share one call.  ``max_new_tokens`` (the largest count)
     is read back from ``cu_seqlens`` when not given, which synchronises with the device.  Returns ``[T*Hq, D]``.
     """
-    for name, t in (("q_prompt", q_prompt), ("k_prompt", k_prompt), ("v_prompt", v_prompt),
-                    ("k_cache_paged", k_cache_paged), ("v_cache_paged", v_cache_paged), ("page_table", page_table),
-                    ("context_len_arr", context_len_arr), ("cu_seqlens", cu_seqlens)):
-        _need_cuda(name, t)
-    if v_cache_paged.dim() != 4 or k_cache_paged.dim() != 5:
-        raise ValueError("k_cache_paged must be 5-D and v_cache_paged 4-D")
-    num_pages, hkv, d, tpp = v_cache_paged.shape
-    if q_prompt.dim() != 3 or k_prompt.dim() != 3 or v_prompt.dim() != 3:
-        raise ValueError("q_prompt, k_prompt and v_prompt must be 3-D [tokens, heads, head_dim]")
-    if not (q_prompt.dtype == k_prompt.dtype == v_prompt.dtype == k_cache_paged.dtype == v_cache_paged.dtype):
-        raise ValueError("all data tensors must share one dtype")
-    total, hq, dq = q_prompt.shape
-    if dq != d or tuple(k_prompt.shape) != (total, hkv, d) or tuple(v_prompt.shape) != (total, hkv, d):
-        raise ValueError("prompt tensor shapes do not match the cache (expected k/v [tokens, kv_heads, head_dim])")
-    if page_table.dim() != 2:
-        raise ValueError("page_table must be 2-D [num_sequences, max_logical_pages]")
-    S = context_len_arr.numel()
+    _need_cuda("cu_seqlens", cu_seqlens)
+    S, total, hq, hkv, d, tpp, num_pages = _prefill_shapes(q_prompt, k_prompt, v_prompt, k_cache_paged, v_cache_paged,
+                                                           page_table, context_len_arr)
     if cu_seqlens.dim() != 1 or cu_seqlens.numel() != S + 1:
         raise ValueError("cu_seqlens must hold num_sequences + 1 row offsets")
-    if page_table.shape[0] < S:
-        raise ValueError("page_table has fewer rows than there are sequences")
-    if hq % hkv != 0:
-        raise ValueError(f"num_q_heads ({hq}) must be a multiple of num_kv_heads ({hkv})")
     dev = q_prompt.device
-    out = torch.empty((total * hq, d), dtype=q_prompt.dtype, device=dev)
-    if total == 0 or S == 0:
-        return out
-    cu = _index32("cu_seqlens", cu_seqlens)
-    if max_new_tokens is None:
-        max_new_tokens = int((cu[1:] - cu[:-1]).max().item())
-    q, k, v = _contig(q_prompt), _contig(k_prompt), _contig(v_prompt)
-    if not (k_cache_paged.is_contiguous() and v_cache_paged.is_contiguous()):
-        raise ValueError("the page pools must be contiguous")
-    pt = _index32("page_table", page_table)
-    ctx = _index32("context_len_arr", context_len_arr)
-    with _on(dev):
-        sp = _stream_ptr(stream, dev)
-        ws = _workspace(lib.pal_prefill_workspace_bytes(S, int(max_new_tokens), hq, hkv, d), dev, sp)
+    code, odt = _out_code(q_prompt.dtype, out_dtype)
+    with _Scope(dev, stream) as sp:
+        out = torch.empty((total * hq, d), dtype=odt, device=dev)
+        if total == 0 or S == 0:
+            return out
+        cu = _index32("cu_seqlens", cu_seqlens)
+        if max_new_tokens is None:
+            max_new_tokens = int((cu[1:] - cu[:-1]).max().item())
+        q, k, v = _contig(q_prompt), _contig(k_prompt), _contig(v_prompt)
+        pt = _index32("page_table", page_table)
+        ctx = _index32("context_len_arr", context_len_arr)
+        ws = _workspace(256, dev, sp)
         rc = lib.pal_paged_attention_prefill_ragged(q.data_ptr(), k.data_ptr(), v.data_ptr(), _ptr(k_cache_paged),
                                                     _ptr(v_cache_paged), _ptr(pt), ctx.data_ptr(), cu.data_ptr(), out.data_ptr(),
                                                     S, total, int(max_new_tokens), hq, hkv, d, tpp, num_pages, pt.shape[1],
-                                                    0.0 if scale is None else float(scale), _dtype_code(q.dtype),
+                                                    0.0 if scale is None else float(scale), code,
                                                     PREFILL_IMPL[impl] if isinstance(impl, str) else int(impl), ws.data_ptr(),
                                                     ws.numel(), sp)
         _lib.check(rc)

@@ -50,28 +50,41 @@ def context_slice(num_pages: int, world_size: int, rank: int) -> range:
 def all_gather_partials(m: torch.Tensor, l: torch.Tensor, acc: torch.Tensor, group=None):
     """All-gather one ``(m [R], l [R], acc [R, D])`` triple per rank into ``[world, ...]`` stacks.
 
-    The three tensors travel as one packed buffer ``[R, D + 2]`` so that the exchange is a single
-    collective (it is latency-bound: 266 KB per GPU for batch 8 x 64 heads x D = 128).
+    Convenience form for callers that hold the three tensors separately; it packs, gathers and unpacks with
+    several small copies.  The hot path is :func:`all_gather_packed`, which moves the buffer the kernel wrote.
     """
     world = dist.get_world_size(group)
     rows, d = acc.shape[:-1], acc.shape[-1]
     packed = torch.cat([acc.reshape(-1, d), m.reshape(-1, 1), l.reshape(-1, 1)], dim=1).contiguous()
-    flat = torch.empty((world * packed.shape[0], packed.shape[1]), dtype=packed.dtype, device=packed.device)
-    dist.all_gather_into_tensor(flat, packed, group=group)
-    out = flat.view(world, packed.shape[0], packed.shape[1])
+    out = all_gather_packed(packed, group=group)
     acc_all = out[:, :, :d].reshape((world,) + tuple(rows) + (d,))
     m_all = out[:, :, d].reshape((world,) + tuple(rows))
     l_all = out[:, :, d + 1].reshape((world,) + tuple(rows))
     return m_all.contiguous(), l_all.contiguous(), acc_all.contiguous()
 
 
+def all_gather_packed(packed: torch.Tensor, out: torch.Tensor = None, group=None) -> torch.Tensor:
+    """One collective for the whole exchange: every rank contributes its packed ``[rows, D + 2]`` partials (``acc``, then
+    ``m``, then ``l`` per row, as ``paged_attention_decode_partials(..., packed=True)`` writes them) and receives
+    ``[world, rows, D + 2]``, which ``lse_combine_packed`` reads in place.  The payload is small (266 KB per GPU for batch
+    8 x 64 heads x D = 128), so the step is latency-bound: nothing is copied before or after the collective."""
+    world = dist.get_world_size(group)
+    if out is None:
+        out = torch.empty((world,) + tuple(packed.shape), dtype=packed.dtype, device=packed.device)
+    dist.all_gather_into_tensor(out.view(world * packed.shape[0], packed.shape[1]), packed, group=group)
+    return out
+
+
 def decode_context_parallel(partials_fn: Callable[[], tuple], combine_fn: Callable, group=None):
     """Long-context decode with the context of every sequence sliced across the ranks of ``group``.
 
-    ``partials_fn()`` returns this rank's ``(m, l, acc)`` over its slice (on GPUs:
-    ``paged_attention_decode_partials``); ``combine_fn(m_all, l_all, acc_all)`` merges the gathered
-    stacks along their leading axis (on GPUs: ``lse_combine``).  Every rank ends up with the full result.
+    ``partials_fn()`` returns this rank's partials over its slice: either the packed ``[rows, D + 2]`` buffer of
+    ``paged_attention_decode_partials(..., packed=True)`` - then ``combine_fn(gathered)`` gets the ``[world, rows, D + 2]``
+    stack (on GPUs: ``lse_combine_packed``) - or a ``(m, l, acc)`` triple, then ``combine_fn(m_all, l_all, acc_all)`` gets the
+    three stacks (``lse_combine``).  Every rank ends up with the full result.
     """
-    m, l, acc = partials_fn()
-    m_all, l_all, acc_all = all_gather_partials(m, l, acc, group=group)
+    part = partials_fn()
+    if isinstance(part, torch.Tensor):
+        return combine_fn(all_gather_packed(part, group=group))
+    m_all, l_all, acc_all = all_gather_partials(*part, group=group)
     return combine_fn(m_all, l_all, acc_all)

@@ -92,3 +92,61 @@ def to_dev(case, device):
 
 def max_abs(a, b):
     return (a.float() - b.float()).abs().max().item() if a.numel() else 0.0
+
+
+# ------------------------------------------------------------------------------------------------
+# the parity rule
+# ------------------------------------------------------------------------------------------------
+TOL = 2e-3  # max-abs against the fp32 oracle, for 16-bit inputs with fp32 accumulation
+
+
+def ulp_distance(a16: torch.Tensor, b16: torch.Tensor) -> torch.Tensor:
+    """Distance in units in the last place between two tensors of one 16-bit float type (same-sign values:
+    the difference of their bit patterns; across zero: the sum of both magnitudes' patterns)."""
+    ia = a16.contiguous().view(torch.int16).to(torch.int32)
+    ib = b16.contiguous().view(torch.int16).to(torch.int32)
+    # map sign-magnitude patterns onto a monotone integer line
+    ka = torch.where(ia < 0, -(ia & 0x7FFF), ia)
+    kb = torch.where(ib < 0, -(ib & 0x7FFF), ib)
+    return (ka - kb).abs()
+
+
+def parity_report(out: torch.Tensor, ref32: torch.Tensor):
+    """Compare a kernel output with the fp32 oracle.
+
+    float32 outputs: every element must be within TOL (plain max-abs).
+    16-bit outputs: an element passes when it is within TOL of the fp32 oracle, or within one unit in the last
+    place (by bit pattern) of the oracle rounded to the output type - rounding a result of magnitude >= 0.5 to
+    bf16 alone moves it by more than TOL.
+    Returns (ok, message); the message carries both max-abs figures and lists the elements that needed the
+    second clause.
+    """
+    out = out.detach().cpu()
+    ref32 = ref32.detach().cpu().float().reshape(out.shape)
+    if out.numel() == 0:
+        return True, "empty"
+    if not torch.isfinite(out.float()).all():
+        return False, "non-finite values in the output"
+    diff = (out.float() - ref32).abs()
+    max_abs_fp32 = diff.max().item()
+    if out.dtype == torch.float32:
+        return max_abs_fp32 <= TOL, f"max-abs vs fp32 oracle {max_abs_fp32:.3e} (float32 output, limit {TOL})"
+    ref16 = ref32.to(out.dtype)
+    max_abs_rounded = (out.float() - ref16.float()).abs().max().item()
+    over = diff > TOL
+    n_over = int(over.sum())
+    msg = f"max-abs vs fp32 oracle {max_abs_fp32:.3e}, vs oracle rounded to {out.dtype} {max_abs_rounded:.3e}"
+    if n_over == 0:
+        return True, msg
+    dist = ulp_distance(out[over], ref16[over])
+    bad = int((dist > 1).sum())
+    mags = ref32[over].abs()
+    msg += (f"; {n_over} elements beyond {TOL} pass by the 1-ulp clause only if their distance <= 1 "
+            f"(|ref| from {mags.min().item():.3f} to {mags.max().item():.3f}, largest distance {int(dist.max())} ulp, {bad} fail)")
+    return bad == 0, msg
+
+
+def assert_parity(out, ref32, what=""):
+    ok, msg = parity_report(out, ref32)
+    assert ok, f"{what}: {msg}" if what else msg
+    return msg

@@ -91,3 +91,54 @@ def test_cpu_tensors_are_rejected():
         pal.paged_attention_decode(q, k, v, torch.zeros((1, 1), dtype=torch.int32), torch.ones(1, dtype=torch.int32))
     with pytest.raises(RuntimeError, match="no CPU path"):
         pal.fill_kv_pages(q, q, k, v, torch.zeros(1, dtype=torch.int64))
+
+
+def test_validators_are_reentrant_from_several_threads():
+    """Argument validation, error strings and the one-time set-up guards can be used from many host threads at once:
+    every thread sees its own error message (thread-local), and no call reaches a device."""
+    import threading
+
+    from proxy_attention_lab_b200 import _lib
+
+    lib = _lib.lib
+    errors = []
+
+    def worker(i):
+        try:
+            dummy = ctypes.create_string_buffer(64)
+            for k in range(300):
+                if (i + k) % 2:
+                    rc = lib.pal_paged_attention_decode(None, None, None, None, None, ctypes.addressof(dummy), 1, 3, 2, 64, 16, 1, 1,
+                                                        0.0, 0, 0, None, 0, None)
+                    assert rc == _lib.PAL_ERR_BAD_ARG and "multiple" in _lib.last_error(), _lib.last_error()
+                else:
+                    rc = lib.pal_get_k_cache_stripe_size(7 + i)
+                    assert rc == _lib.PAL_ERR_UNSUPPORTED and f"dtype {7 + i}" in _lib.last_error(), _lib.last_error()
+                assert lib.pal_decode_workspace_bytes(8, 64, 8, 128, 16, 8192, 0) == 256
+                assert lib.pal_set_wait_limit_cycles(0) > 0
+        except Exception as e:  # noqa: BLE001
+            errors.append(repr(e))
+
+    threads = [threading.Thread(target=worker, args=(i,)) for i in range(8)]
+    for t in threads:
+        t.start()
+    for t in threads:
+        t.join()
+    assert not errors, errors
+
+
+def test_out_f32_flag_and_new_entry_points_validate():
+    from proxy_attention_lab_b200 import _lib
+
+    lib = _lib.lib
+    # the flag is accepted together with a valid element type and refused with an invalid one
+    assert lib.pal_paged_attention_decode(None, None, None, None, None, None, 0, 2, 2, 64, 16, 1, 1, 0.0, _lib.PAL_OUT_F32 | 1, 0,
+                                          None, 0, None) == _lib.PAL_OK
+    assert lib.pal_paged_attention_decode(None, None, None, None, None, None, 0, 2, 2, 64, 16, 1, 1, 0.0, _lib.PAL_OUT_F32 | 5, 0,
+                                          None, 0, None) == _lib.PAL_ERR_UNSUPPORTED
+    assert lib.pal_lse_combine_packed(None, None, 2, 4, 64, 1, None) == _lib.PAL_ERR_BAD_ARG
+    assert lib.pal_lse_combine_packed(None, None, 2, 0, 64, 1, None) == _lib.PAL_OK
+    assert lib.pal_workspace_init(None, 0, None) == _lib.PAL_ERR_WORKSPACE
+    assert lib.pal_check_status(None, None) == _lib.PAL_ERR_BAD_ARG
+    rc = lib.pal_paged_attention_decode_partials_packed(None, None, None, None, None, None, 1, 2, 2, 64, 16, 1, 1, 0.0, 0, 0, None, 0, None)
+    assert rc == _lib.PAL_ERR_BAD_ARG and "partition_pages" in _lib.last_error()

@@ -8,7 +8,7 @@ call the newest token's slot holds NaN, so an output that read the pool instead 
 import pytest
 import torch
 
-from cases import make_decode_case, uniform_lengths
+from cases import assert_parity, make_decode_case, uniform_lengths
 from oracle import decode_oracle
 
 pytestmark = pytest.mark.gpu
@@ -48,11 +48,7 @@ def _check(pal, cuda, case, partition_pages):
     out, k_after, v_after = _run(pal, cuda, case, partition_pages)
     # the pools end up exactly as fill_kv_pages leaves them (case.k_pool / v_pool were packed with every token)
     assert _bit_equal(k_after, case.k_pool) and _bit_equal(v_after, case.v_pool)
-    assert torch.isfinite(out.float()).all()
-    diff = (out.float() - ref).abs()
-    ulp = torch.maximum(ref.abs(), torch.tensor(1e-3)) * (2.0 ** -7 if out.dtype == torch.bfloat16 else 2.0 ** -10)
-    bad = (diff > TOL) & (diff > ulp)
-    assert not bad.any(), f"max-abs {diff.max().item()}, {int(bad.sum())} elements out of tolerance"
+    assert_parity(out, ref, "fused append + decode")
 
 
 @pytest.mark.parametrize("partition_pages", [0, None, 4])

@@ -5,16 +5,25 @@ invariance, linearity of the log-sum-exp combine, agreement of the two prefill k
 import pytest
 import torch
 
+from cases import parity_report
 from oracle import decode_oracle, prefill_oracle
 
 pytestmark = pytest.mark.gpu
 TOL = 2e-3
 
 
-def within(out, ref, dtype=torch.bfloat16):
-    diff = (out.float().cpu() - ref.float().cpu()).abs()
-    ulp = ref.float().cpu().abs() * (2.0 ** -7 if dtype == torch.bfloat16 else 2.0 ** -10)
-    return bool(((diff <= TOL) | (diff <= ulp)).all()), diff.max().item()
+def within(out, ref):
+    """Against the fp32 oracle (cases.parity_report): float32 outputs by plain max-abs <= 2e-3, 16-bit outputs with the
+    one-unit-in-the-last-place clause for elements whose rounding alone exceeds that."""
+    return parity_report(out, ref)
+
+
+def close(a, b):
+    """Two kernel results of one output type that must agree: each is within tolerance of the oracle, so their distance is
+    bounded by twice that plus one rounding step of the larger magnitude."""
+    a, b = a.float().cpu(), b.float().cpu()
+    diff = (a - b).abs()
+    return bool((diff <= 2 * TOL + b.abs() * 2.0 ** -7).all()), diff.max().item()
 
 
 def build_decode(cuda, S, lo, hi, hq, hkv, seed=0, d=128, tpp=16):
@@ -58,8 +67,13 @@ def test_llama8b_decode_batch_full(pal, cuda):
     ref = oracle_decode_slice(q, kp, vp, table, lens, seqs, list(range(8)), 4)
     ok, err = within(out[seqs], ref)
     assert ok, err
+    out32 = pal.paged_attention_decode(q, kp, vp, table, lens, partition_pages=0, out_dtype=torch.float32)
+    ok, err = within(out32[seqs], ref)
+    assert ok, err
     # two-pass gives the same answer on the whole batch
-    ok, err = within(pal.paged_attention_decode(q, kp, vp, table, lens, partition_pages=64), out)
+    ok, err = close(pal.paged_attention_decode(q, kp, vp, table, lens, partition_pages=64), out)
+    assert ok, err
+    ok, err = close(pal.paged_attention_decode(q, kp, vp, table, lens, partition_pages=64, out_dtype=torch.float32), out32)
     assert ok, err
     # the order of the sequences in the batch does not change any sequence's result (bit for bit)
     perm = torch.randperm(64, generator=torch.Generator().manual_seed(3)).to(cuda)
@@ -75,9 +89,12 @@ def test_llama70b_long_decode_full(pal, cuda):
     got = torch.cat([out[3:4, 0:8], out[3:4, 40:48]], dim=1)
     ok, err = within(got, ref)
     assert ok, err
-    # single pass and a different partition size agree with it
-    for pp in (0, 1024):
-        ok, err = within(pal.paged_attention_decode(q, kp, vp, table, lens, partition_pages=pp), out)
+    out32 = pal.paged_attention_decode(q, kp, vp, table, lens, partition_pages=256, out_dtype=torch.float32)
+    ok, err = within(torch.cat([out32[3:4, 0:8], out32[3:4, 40:48]], dim=1), ref)
+    assert ok, err
+    # single pass, a different partition size and the launcher's own choice agree with it
+    for pp in (0, 1024, None):
+        ok, err = close(pal.paged_attention_decode(q, kp, vp, table, lens, partition_pages=pp), out)
         assert ok, err
     # linearity of the combine: partials over the two halves of every context merge to the full result
     half = table.shape[1] // 2
@@ -85,8 +102,13 @@ def test_llama70b_long_decode_full(pal, cuda):
     m1, l1, a1 = pal.paged_attention_decode_partials(q, kp, vp, table[:, :half].contiguous(), torch.minimum(lens, zeros + half * 16), partition_pages=256)
     m2, l2, a2 = pal.paged_attention_decode_partials(q, kp, vp, table[:, half:].contiguous(), torch.clamp(lens - half * 16, min=0), partition_pages=256)
     merged = pal.lse_combine(torch.stack([m1, m2]), torch.stack([l1, l2]), torch.stack([a1, a2]), out_dtype=torch.bfloat16)
-    ok, err = within(merged, out)
+    ok, err = close(merged, out)
     assert ok, err
+    # the packed form of the same exchange: one [rows, D + 2] buffer per half, merged in place
+    p1 = pal.paged_attention_decode_partials(q, kp, vp, table[:, :half].contiguous(), torch.minimum(lens, zeros + half * 16), partition_pages=256, packed=True)
+    p2 = pal.paged_attention_decode_partials(q, kp, vp, table[:, half:].contiguous(), torch.clamp(lens - half * 16, min=0), partition_pages=256, packed=True)
+    merged_p = pal.lse_combine_packed(torch.stack([p1, p2]), out_dtype=torch.bfloat16, out_shape=out.shape)
+    assert torch.equal(merged_p, merged)
 
 
 def test_chunked_prefill_full(pal, cuda):
@@ -111,6 +133,7 @@ def test_chunked_prefill_full(pal, cuda):
     q, k, v = mk(S * N, hq, d), mk(S * N, hkv, d), mk(S * N, hkv, d)
     table, hist_d = table.to(cuda), hist.to(torch.int32).to(cuda)
     out = pal.paged_attention_prefill(q, k, v, kp, vp, table, hist_d, impl="tcgen05").reshape(S, N, hq, d)
+    out32 = pal.paged_attention_prefill(q, k, v, kp, vp, table, hist_d, impl="tcgen05", out_dtype=torch.float32).reshape(S, N, hq, d)
     # oracle on two whole sequences, one kv head (4 query heads) each
     for s, kvh in ((1, 0), (2, 7)):
         n = int(npg[s])
@@ -119,6 +142,8 @@ def test_chunked_prefill_full(pal, cuda):
                              v[s * N:(s + 1) * N, kvh:kvh + 1].cpu(), kp[pages][:, kvh:kvh + 1].cpu(), vp[pages][:, kvh:kvh + 1].cpu(),
                              torch.arange(max(n, 1), dtype=torch.int32).reshape(1, -1)[:, :n], hist[s:s + 1].to(torch.int32))
         ok, err = within(out[s, :, kvh * 4:(kvh + 1) * 4].reshape(N * 4, d), ref)
+        assert ok, (s, err)
+        ok, err = within(out32[s, :, kvh * 4:(kvh + 1) * 4].reshape(N * 4, d), ref)
         assert ok, (s, err)
     # the mma.sync kernel agrees with it on the whole batch (each is within tolerance of the oracle,
     # so their distance is bounded by twice that)

@@ -5,6 +5,7 @@ import os
 import pytest
 import torch
 
+from cases import assert_parity
 from oracle import decode_oracle, fill_kv_pages_oracle, prefill_oracle
 
 VECTORS = torch.load(os.path.join(os.path.dirname(__file__), "golden", "vectors.pt"))
@@ -30,16 +31,16 @@ def test_oracle_reproduces_golden(name):
 @pytest.mark.gpu
 @pytest.mark.parametrize("name", NAMES)
 def test_kernels_match_golden(pal, cuda, name):
-    tol = 2e-3
     d = {k: v.to(cuda) for k, v in VECTORS[f"decode_{name}"].items()}
     for pp in (0, 2):
         out = pal.paged_attention_decode(d["q"], d["k_pool"], d["v_pool"], d["page_table"], d["lens"], partition_pages=pp)
-        diff = (out.float() - d["expected"]).abs()
-        assert ((diff <= tol) | (diff <= d["expected"].abs() * 2.0 ** -7)).all(), diff.max().item()
+        assert_parity(out, d["expected"], f"decode_{name}, partition_pages={pp}")
     p = {k: v.to(cuda) for k, v in VECTORS[f"prefill_{name}"].items()}
     out = pal.paged_attention_prefill(p["q"], p["k_new"], p["v_new"], p["k_pool"], p["v_pool"], p["page_table"], p["hist"])
-    diff = (out.float() - p["expected"]).abs()
-    assert ((diff <= tol) | (diff <= p["expected"].abs() * 2.0 ** -7)).all(), diff.max().item()
+    assert_parity(out, p["expected"], f"prefill_{name}")
+    out32 = pal.paged_attention_prefill(p["q"], p["k_new"], p["v_new"], p["k_pool"], p["v_pool"], p["page_table"], p["hist"],
+                                        out_dtype=torch.float32)
+    assert_parity(out32, p["expected"], f"prefill_{name}, float32 output")
     f = {k: v.to(cuda) for k, v in VECTORS[f"fill_{name}"].items()}
     gk, gv = pal.fill_kv_pages(f["keys"], f["vals"], f["k_pool"].clone(), f["v_pool"].clone(), f["slots"])
     assert bit_equal(gk, f["expected_k"]) and bit_equal(gv, f["expected_v"])

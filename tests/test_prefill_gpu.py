@@ -3,7 +3,7 @@
 import pytest
 import torch
 
-from cases import make_prefill_case, max_abs, to_dev
+from cases import assert_parity, make_prefill_case, max_abs, to_dev
 from oracle import prefill_oracle
 
 pytestmark = pytest.mark.gpu
@@ -22,18 +22,17 @@ def supported(impl, d, tpp=16):
     return impl == "mma" or (d == 128 and tpp == 16)
 
 
-def check(pal, cuda, case, impl, tol=TOL):
+def check(pal, cuda, case, impl):
+    """float32 output: plain max-abs <= 2e-3 on every element.  16-bit output: early causal rows attend to one or two
+    keys, so |out| reaches a few units and the rounding of the output alone exceeds 2e-3; those elements must sit
+    within one unit in the last place of the oracle rounded to the output type (cases.parity_report)."""
     ref = prefill_oracle(case.q, case.k_new, case.v_new, case.k_pool, case.v_pool, case.page_table, case.hist)
+    out32 = run_prefill(pal, case, cuda, impl=impl, out_dtype=torch.float32)
+    assert out32.shape == ref.shape and out32.dtype == torch.float32
+    assert_parity(out32, ref, f"{impl}, float32 output")
     out = run_prefill(pal, case, cuda, impl=impl)
     assert out.shape == ref.shape and out.dtype == case.q.dtype
-    assert torch.isfinite(out.float()).all()
-    # Early causal rows attend to one or two keys, so |out| reaches a few units and the rounding of the
-    # 16-bit output alone exceeds 2e-3; the kernel is therefore also compared with the oracle rounded to
-    # the output dtype, allowing one unit in the last place there.
-    diff = (out.float() - ref).abs()
-    ulp = torch.maximum(ref.abs(), torch.tensor(1e-3)) * (2.0 ** -7 if out.dtype == torch.bfloat16 else 2.0 ** -10)
-    bad = (diff > tol) & (diff > ulp)
-    assert not bad.any(), f"max-abs {diff.max().item()} with {int(bad.sum())} elements out of tolerance"
+    assert_parity(out, ref, f"{impl}, 16-bit output")
 
 
 IMPLS = ["mma", "tcgen05"]  # tcgen05 covers head_dim 128 / tokens_per_page 16

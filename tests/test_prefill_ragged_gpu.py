@@ -3,7 +3,7 @@
 import pytest
 import torch
 
-from cases import make_decode_case
+from cases import assert_parity, make_decode_case
 from oracle import prefill_ragged_oracle
 
 pytestmark = pytest.mark.gpu
@@ -33,13 +33,10 @@ def run(pal, cuda, c, **kw):
 
 def check(pal, cuda, c, impl):
     ref = prefill_ragged_oracle(c["q"], c["k"], c["v"], c["k_pool"], c["v_pool"], c["table"], c["hist"], c["cu"])
+    assert_parity(run(pal, cuda, c, impl=impl, out_dtype=torch.float32), ref, f"{impl}, float32 output")
     out = run(pal, cuda, c, impl=impl)
     assert out.shape == ref.shape and out.dtype == c["q"].dtype
-    assert torch.isfinite(out.float()).all()
-    diff = (out.float() - ref).abs()
-    ulp = torch.maximum(ref.abs(), torch.tensor(1e-3)) * (2.0 ** -7 if out.dtype == torch.bfloat16 else 2.0 ** -10)
-    bad = (diff > TOL) & (diff > ulp)
-    assert not bad.any(), f"max-abs {diff.max().item()} with {int(bad.sum())} elements out of tolerance"
+    assert_parity(out, ref, f"{impl}, 16-bit output")
 
 
 @pytest.mark.parametrize("impl", IMPLS)
@@ -81,10 +78,7 @@ def test_auto_choice_and_explicit_maximum(pal, cuda):
     c = make_ragged_case(15, [64, 0, 700], counts, 32, 8, 128)
     ref = prefill_ragged_oracle(c["q"], c["k"], c["v"], c["k_pool"], c["v_pool"], c["table"], c["hist"], c["cu"])
     for kw in (dict(), dict(max_new_tokens=256), dict(max_new_tokens=300)):
-        out = run(pal, cuda, c, **kw)
-        diff = (out.float() - ref).abs()
-        ulp = torch.maximum(ref.abs(), torch.tensor(1e-3)) * 2.0 ** -7
-        assert not ((diff > TOL) & (diff > ulp)).any()
+        assert_parity(run(pal, cuda, c, **kw), ref, str(kw))
 
 
 def test_empty_batch(pal, cuda):

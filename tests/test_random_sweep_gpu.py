@@ -7,7 +7,7 @@ import random
 import pytest
 import torch
 
-from cases import make_decode_case
+from cases import make_decode_case, parity_report
 from oracle import decode_oracle, fill_kv_pages_oracle, prefill_ragged_oracle, slots_from_page_table
 from oracle import k_cache_shape, v_cache_shape
 
@@ -18,10 +18,7 @@ HEAD_DIMS = [32, 64, 80, 96, 128, 256]
 
 
 def _within(out, ref):
-    diff = (out.float() - ref).abs()
-    ulp = torch.maximum(ref.abs(), torch.tensor(1e-3)) * (2.0 ** -7 if out.dtype == torch.bfloat16 else 2.0 ** -10)
-    bad = (diff > TOL) & (diff > ulp)
-    return not bad.any(), f"max-abs {diff.max().item() if diff.numel() else 0.0}, {int(bad.sum())} out of tolerance"
+    return parity_report(out, ref)
 
 
 def _interesting_length(rng, tpp, hi):
