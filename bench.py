@@ -2,9 +2,16 @@
 """Benchmark of the paged-attention hot path on B200.
 
 ``python bench.py --gpus N --steps K --warmup W`` prints ONE JSON line (rank 0).  A step is one pass
-of the operator over one batch of synthetic input already resident in HBM.  The default workload is
-the Llama-3-8B-shaped decode batch the headline metric (paged decode KV GB/s) is quoted on; other
-workloads (``--workload decode_70b | prefill_8b | fill | fill_append``) cover the remaining configurations.
+of the operator over one batch of synthetic input already resident in HBM.  The headline workload is
+the Llama-3-8B-shaped decode batch the metric (paged decode KV GB/s) is quoted on; the same line carries,
+under ``workloads``, one record each for the other parts of the metric - chunked prefill (TFLOP/s), the
+Llama-3-70B long-context two-pass decode, fill_kv_pages - and, under torchrun, the multi-GPU forms of the long
+decode (kv-head sharded; context sharded with the NCCL all-gather + combine; context sharded with the fused
+peer-store exchange).  ``--workload NAME`` makes another workload the headline; ``--workloads none`` leaves the
+extra records out (profiler captures use that).
+
+Every figure is the median over ``--blocks`` timed blocks of K steps each (barrier + synchronize around every
+block, CUDA events on the launching stream, max over ranks); the fastest block is reported beside it.
 
 ``--impl reference`` times the reference side of the comparison instead.  Proxy Attention Lab has no
 CPU implementation and its Metal kernels cannot run here, so that arm is the CPU oracle (the
@@ -43,9 +50,15 @@ WORKLOADS = {
                                      desc="latency case as two calls, fill_kv_pages then paged_attention_decode: batch 4, context U[64,512], 8q/2kv heads, D=128, bf16, TPP=16"),
     "decode_70b": dict(kind="decode", S=8, lo=131072, hi=131072, hq=64, hkv=8, d=128, tpp=16, partition_pages=256,
                        desc="Llama-3-70B long decode: batch 8, context 131072, 64q/8kv heads, D=128, bf16, TPP=16, two-pass 256-page partitions"),
-    "decode_70b_ctx": dict(kind="decode", S=8, lo=131072, hi=131072, hq=64, hkv=8, d=128, tpp=16, partition_pages=256, ctx_sharded=True,
+    "decode_70b_auto": dict(kind="decode", S=8, lo=131072, hi=131072, hq=64, hkv=8, d=128, tpp=16, partition_pages=-1,
+                            desc="Llama-3-70B long decode: batch 8, context 131072, 64q/8kv heads, D=128, bf16, TPP=16, two-pass with the partition size "
+                                 "chosen by the launcher from the work items per SM"),
+    "decode_70b_ctx": dict(kind="decode", S=8, lo=131072, hi=131072, hq=64, hkv=8, d=128, tpp=16, partition_pages=256, ctx="nccl",
                            desc="Llama-3-70B long decode, context sharded: batch 8, context 131072 cut into N contiguous slices (one per GPU), "
                                 "64q/8kv heads, D=128, bf16, TPP=16, 256-page partitions, per-GPU (m,l,acc) all-gathered over NCCL and merged"),
+    "decode_70b_ctx_fused": dict(kind="decode", S=8, lo=131072, hi=131072, hq=64, hkv=8, d=128, tpp=16, partition_pages=256, ctx="fused",
+                                 desc="Llama-3-70B long decode, context sharded: batch 8, context 131072 cut into N contiguous slices (one per GPU), "
+                                      "64q/8kv heads, D=128, bf16, TPP=16, 256-page partitions, per-GPU (m,l,acc) exchanged by peer stores inside the combine kernel"),
     "prefill_8b": dict(kind="prefill", S=8, n=2048, hlo=0, hhi=4096, hq=32, hkv=8, d=128, tpp=16,
                        desc="Llama-3-8B chunked causal prefill: 8 x 2048 new tokens, history U[0,4096], 32q/8kv heads, D=128, bf16, TPP=16"),
     "prefill_small": dict(kind="prefill", S=2, n=1024, hlo=0, hhi=2048, hq=32, hkv=8, d=128, tpp=16,
@@ -77,7 +90,7 @@ def measured_peaks():
 class ClockSampler:
     """Samples SM clock and throttle reasons through NVML (read-only) while a region runs."""
 
-    def __init__(self, index: int, period_s: float = 0.01):
+    def __init__(self, index: int, period_s: float = 0.002):
         self.index, self.period = index, period_s
         self.samples, self.reasons = [], set()
         self.max_mhz = None
@@ -170,12 +183,17 @@ def build_decode(cfg, device, seed, hkv_local=None):
     total_tokens = int(lens.sum())
     kv_bytes = total_tokens * hkv * d * 2 * 2
     alg_bytes = kv_bytes + 2 * cfg["S"] * hq_local * d * 2 + 4 * int(npg.sum()) + 4 * cfg["S"]
-    if cfg["partition_pages"]:
-        parts = (MP + cfg["partition_pages"] - 1) // cfg["partition_pages"]
+    pp = cfg["partition_pages"]
+    if pp < 0:  # the launcher's own choice, asked from the library
+        from proxy_attention_lab_b200 import _lib
+
+        pp = _lib.lib.pal_decode_auto_partition_pages(cfg["S"], hq_local, hkv, d, tpp, MP)
+    if pp:
+        parts = (MP + pp - 1) // pp
         alg_bytes += 2 * cfg["S"] * hq_local * parts * (d + 2) * 4
     return dict(k_pool=k_pool, v_pool=v_pool, q_host=q_host, table_host=table_host, lens_host=lens_host,
                 q=q_host.to(device), table=table_host.to(device), lens=lens_host.to(device), kv_bytes=kv_bytes,
-                alg_bytes=alg_bytes, tokens=cfg["S"], hq=hq_local, hkv=hkv, lens_cpu=lens)
+                alg_bytes=alg_bytes, tokens=cfg["S"], hq=hq_local, hkv=hkv, lens_cpu=lens, partition_pages=pp)
 
 
 def build_prefill(cfg, device, seed, seqs=None):
@@ -235,8 +253,10 @@ def build_fill(cfg, device, seed):
 # ------------------------------------------------------------------------------------------------
 # CPU side (oracle) - the reference arm and the cpu_baseline leg
 # ------------------------------------------------------------------------------------------------
-def cpu_decode_sample(cfg, budget_s, seed=0):
-    """Times the oracle on the first sequences of the workload until `budget_s` is spent. Returns (bytes, seconds, n_seqs)."""
+def cpu_decode_sample(cfg, budget_s, seed=0, data=None):
+    """Times the oracle on the first sequences of the workload until `budget_s` is spent. Returns (bytes, seconds, n_seqs).
+    With `data` (the GPU arm's batch) the sequences' own pages and queries are copied to the host; otherwise data of the
+    same shapes is drawn from a seeded generator."""
     from oracle import decode_oracle
 
     tpp, d, hq, hkv = cfg["tpp"], cfg["d"], cfg["hq"], cfg["hkv"]
@@ -248,10 +268,16 @@ def cpu_decode_sample(cfg, budget_s, seed=0):
         if L * hkv * d * 4 > 8e9:  # keep one sequence's fp32 copy within host memory
             L = int(8e9 // (hkv * d * 4))
         npg = (L + tpp - 1) // tpp
-        k_pool = torch.randn((npg, hkv, d // 8, tpp, 8), generator=g).to(torch.bfloat16)
-        v_pool = torch.randn((npg, hkv, d, tpp), generator=g).to(torch.bfloat16)
-        q = torch.randn((1, hq, d), generator=g).to(torch.bfloat16)
-        table = torch.randperm(npg, generator=g).reshape(1, npg).to(torch.int32)
+        if data is not None:
+            pages = data["table"][s, :npg].long()
+            k_pool, v_pool = data["k_pool"][pages].cpu(), data["v_pool"][pages].cpu()
+            q = data["q"][s:s + 1].cpu()
+            table = torch.arange(npg, dtype=torch.int32).reshape(1, npg)
+        else:
+            k_pool = torch.randn((npg, hkv, d // 8, tpp, 8), generator=g).to(torch.bfloat16)
+            v_pool = torch.randn((npg, hkv, d, tpp), generator=g).to(torch.bfloat16)
+            q = torch.randn((1, hq, d), generator=g).to(torch.bfloat16)
+            table = torch.randperm(npg, generator=g).reshape(1, npg).to(torch.int32)
         t0 = time.perf_counter()
         decode_oracle(q, k_pool, v_pool, table, torch.tensor([L], dtype=torch.int32))
         spent += time.perf_counter() - t0
@@ -262,7 +288,7 @@ def cpu_decode_sample(cfg, budget_s, seed=0):
     return done_bytes, spent, nseq
 
 
-def cpu_prefill_sample(cfg, budget_s, seed=0):
+def cpu_prefill_sample(cfg, budget_s, seed=0, data=None):
     from oracle import prefill_oracle
 
     tpp, d, hq, hkv = cfg["tpp"], cfg["d"], cfg["hq"], cfg["hkv"]
@@ -270,12 +296,19 @@ def cpu_prefill_sample(cfg, budget_s, seed=0):
     hist = int(make_lengths(seed, cfg["S"], cfg["hlo"], cfg["hhi"])[0])
     g = torch.Generator().manual_seed(seed + 7)
     npg = max((hist + tpp - 1) // tpp, 1)
-    k_pool = torch.randn((npg, hkv, d // 8, tpp, 8), generator=g).to(torch.bfloat16)
-    v_pool = torch.randn((npg, hkv, d, tpp), generator=g).to(torch.bfloat16)
-    q = torch.randn((n, hq, d), generator=g).to(torch.bfloat16)
-    k = torch.randn((n, hkv, d), generator=g).to(torch.bfloat16)
-    v = torch.randn((n, hkv, d), generator=g).to(torch.bfloat16)
-    table = torch.randperm(npg, generator=g).reshape(1, npg).to(torch.int32)
+    if data is not None and "cu" not in data:
+        # the first sequence of the GPU arm's batch: its history pages and the first n of its new tokens
+        pages = data["table"][0, :npg].long()
+        k_pool, v_pool = data["k_pool"][pages].cpu(), data["v_pool"][pages].cpu()
+        q, k, v = data["q"][:n].cpu(), data["k"][:n].cpu(), data["v"][:n].cpu()
+        table = torch.arange(npg, dtype=torch.int32).reshape(1, npg)
+    else:
+        k_pool = torch.randn((npg, hkv, d // 8, tpp, 8), generator=g).to(torch.bfloat16)
+        v_pool = torch.randn((npg, hkv, d, tpp), generator=g).to(torch.bfloat16)
+        q = torch.randn((n, hq, d), generator=g).to(torch.bfloat16)
+        k = torch.randn((n, hkv, d), generator=g).to(torch.bfloat16)
+        v = torch.randn((n, hkv, d), generator=g).to(torch.bfloat16)
+        table = torch.randperm(npg, generator=g).reshape(1, npg).to(torch.int32)
     flops, spent, reps = 0, 0.0, 0
     while spent < budget_s:
         t0 = time.perf_counter()
@@ -357,16 +390,19 @@ def metric_of(kind):
     return {"decode": ("paged decode KV GB/s", "GB/s"), "prefill": ("prefill TFLOPS", "TFLOP/s"), "fill": ("fill_kv_pages payload GB/s", "GB/s")}[kind]
 
 
-def cpu_measure(cfg, budget_s):
+def cpu_measure(cfg, budget_s, data=None):
+    """The oracle on a bounded sample of the workload.  `data` = the GPU arm's tensors (the sample is then cut from the very
+    inputs the kernels ran on); without it the sample is seeded N(0,1) data of the same shapes."""
     kind = cfg["kind"]
+    src = "the GPU arm's own tensors" if data is not None else "seeded N(0,1) data of the same shapes (not the GPU arm's tensors)"
     if kind == "decode":
-        nbytes, spent, nseq = cpu_decode_sample(cfg, budget_s)
-        return nbytes / spent / 1e9, f"first {nseq} sequences of the batch ({nbytes / 1e9:.3f} GB of KV)"
+        nbytes, spent, nseq = cpu_decode_sample(cfg, budget_s, data=data)
+        return nbytes / spent / 1e9, f"first {nseq} sequences of the batch ({nbytes / 1e9:.3f} GB of KV), {src}"
     if kind == "prefill":
-        flops, spent, what = cpu_prefill_sample(cfg, budget_s)
-        return flops / spent / 1e12, what
+        flops, spent, what = cpu_prefill_sample(cfg, budget_s, data=data)
+        return flops / spent / 1e12, f"{what}, {src}"
     nbytes, spent, what = cpu_fill_sample(cfg, budget_s)
-    return nbytes / spent / 1e9, what
+    return nbytes / spent / 1e9, f"{what}, seeded N(0,1) data of the same shapes"
 
 
 def run_reference(args, cfg, rank):
@@ -387,7 +423,7 @@ def run_reference(args, cfg, rank):
     value = sum(vals) / len(vals)
     line = {"impl": "reference", "metric": metric, "value": value, "unit": unit, "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": wall / args.steps * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16 storage, f32 arithmetic",
-            "data": "synthetic", "config": {"workload": cfg["desc"]},
+            "data": "synthetic", "config": {"workload": cfg["desc"]}, "blocks": 1,
             "cpu_baseline": {"value": value, "unit": unit, "cores": torch.get_num_threads(), "kind": "port", "sample": f"each step: {what}"},
             "e2e": {"value": value, "unit": unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}, "gpu_launches": 0}
     print(json.dumps(line), flush=True)
@@ -396,69 +432,81 @@ def run_reference(args, cfg, rank):
 # ------------------------------------------------------------------------------------------------
 # GPU side
 # ------------------------------------------------------------------------------------------------
-def main():
-    ap = argparse.ArgumentParser()
-    ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=2000)
-    ap.add_argument("--warmup", type=int, default=10)
-    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="decode_8b", choices=sorted(WORKLOADS))
-    ap.add_argument("--prefill-impl", default="auto")
-    ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--no-cuda-graph", action="store_true", help="context-sharded workload: enqueue every step from the host")
-    args = ap.parse_args()
-    cfg = WORKLOADS[args.workload]
-    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+class Env:
+    """Rank / device / process group of this run, and the barrier every timed block is bracketed with."""
 
-    rank = int(os.environ.get("RANK", "0"))
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
-    if args.impl == "reference":
-        run_reference(args, cfg, rank)
-        return
+    def __init__(self):
+        self.rank = int(os.environ.get("RANK", "0"))
+        self.world = int(os.environ.get("WORLD_SIZE", "1"))
+        self.local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+        self.device = torch.device("cuda", self.local_rank)
+        self.dist = None
 
-    import torch.distributed as dist
+    def init(self):
+        torch.cuda.set_device(self.device)
+        if self.world > 1:
+            import torch.distributed as dist
 
-    import proxy_attention_lab_b200 as pal  # raises if the CUDA library is missing: no fallback
+            dist.init_process_group("nccl", device_id=self.device)
+            self.dist = dist
 
-    if not torch.cuda.is_available():
-        raise RuntimeError("bench.py needs a CUDA device; there is no CPU path")
-    device = torch.device("cuda", local_rank)
-    torch.cuda.set_device(device)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=device)
-
-    def barrier():
-        if world > 1:
-            dist.barrier()
+    def barrier(self):
+        if self.dist is not None:
+            self.dist.barrier()
         torch.cuda.synchronize()
 
-    kind = cfg["kind"]
+    def max_over_ranks(self, x: float) -> float:
+        if self.dist is None:
+            return x
+        t = torch.tensor([x], device=self.device, dtype=torch.float64)
+        self.dist.all_reduce(t, op=self.dist.ReduceOp.MAX)
+        return float(t.item())
+
+    def sum_over_ranks(self, x: float) -> float:
+        if self.dist is None:
+            return x
+        t = torch.tensor([x], device=self.device, dtype=torch.float64)
+        self.dist.all_reduce(t, op=self.dist.ReduceOp.SUM)
+        return float(t.item())
+
+
+class Prepared:
+    """One workload made ready on this rank: the step to time, its end-to-end pipeline and what a step amounts to."""
+
+    def __init__(self, **kw):
+        self.extra_cfg, self.pipe, self.scaling, self.notes = {}, None, "weak", []
+        self.units_are_global = False  # True: every rank reports the whole job's units (strong scaling of one problem)
+        self.__dict__.update(kw)
+
+
+def prepare(name, env, pal, peaks, args, force_single=False):
+    """Build the synthetic inputs of workload `name` on this rank.  `force_single` builds the one-GPU form of the problem on
+    every rank (the N = 1 baseline a strong-scaling record is compared with)."""
+    cfg = WORKLOADS[name]
+    kind, device, rank = cfg["kind"], env.device, env.rank
+    world = 1 if force_single else env.world
     metric, unit = metric_of(kind)
-    peaks = measured_peaks()
-    scaling = "weak"
-    extra_cfg = {}
+    w = Prepared(name=name, cfg=cfg, kind=kind, metric=metric, unit=unit)
     if kind == "decode":
         hkv_local = None
-        ctx = bool(cfg.get("ctx_sharded"))
+        ctx = cfg.get("ctx")  # None | "nccl" | "fused"
+        base = cfg
         if ctx:
-            scaling = "strong"
-            extra_cfg["parallelism"] = f"context sharded x{world}: partials + one NCCL all-gather + LSE combine per step"
+            w.scaling, w.units_are_global = "strong", False
+            how = ("partials + one NCCL all-gather of the packed (acc, m, l) buffer + LSE combine" if ctx == "nccl"
+                   else "split-KV pass + one kernel that stores the merged (acc, m, l) into every peer's buffer over NVLink, waits on flags and combines")
+            w.extra_cfg["parallelism"] = f"context sharded x{world}: {how}"
             cfg = dict(cfg, lo=cfg["lo"] // world, hi=cfg["hi"] // world)  # this rank's slice of every sequence
-        if args.workload == "decode_70b" and world > 1:
+        if name.startswith("decode_70b") and not ctx and world > 1:
             # total work fixed: each GPU owns Hkv/N kv heads (and their query heads) of every sequence
-            hkv_local, scaling = cfg["hkv"] // world, "strong"
-            extra_cfg["parallelism"] = f"kv-head sharded x{world}, no collective"
+            hkv_local, w.scaling = cfg["hkv"] // world, "strong"
+            w.extra_cfg["parallelism"] = f"kv-head sharded x{world}, no collective"
         elif world > 1 and not ctx:
-            extra_cfg["parallelism"] = f"sequence sharded x{world} (each GPU its own batch of {cfg['S']}), no collective"
-        data = build_decode(cfg, device, seed=rank if hkv_local is None else 0, hkv_local=hkv_local)
+            w.extra_cfg["parallelism"] = f"sequence sharded x{world} (each GPU its own batch of {cfg['S']}), no collective"
+        data = build_decode(cfg, device, seed=rank if (hkv_local is None and not ctx) else 0, hkv_local=hkv_local)
         pp = cfg["partition_pages"]
-        if ctx:
-            from proxy_attention_lab_b200.sharding import all_gather_partials
-
-            if world > 1:  # every rank must hold the same queries
-                dist.broadcast(data["q"], src=0)
-
+        if ctx and env.dist is not None and world > 1:
+            env.dist.broadcast(data["q"], src=0)  # every rank must hold the same queries
         append = cfg.get("append")
         if append:
             gen = torch.Generator(device=device).manual_seed(1234 + rank)
@@ -467,6 +515,25 @@ def main():
             new_k_host, new_v_host = new_k.cpu().pin_memory(), new_v.cpu().pin_memory()
             last_pos = (data["lens"] - 1).to(torch.int32)
             seq_ids = torch.arange(cfg["S"], device=device, dtype=torch.int32)
+        xchg = gathered = None
+        rows = cfg["S"] * data["hq"]
+        if ctx == "fused":
+            from proxy_attention_lab_b200.sharding import ContextExchange
+
+            if env.dist is None:
+                import torch.distributed as dist
+
+                # a single process still needs a (one-rank) group for the symmetric-memory rendezvous
+                os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+                os.environ.setdefault("MASTER_PORT", "29533")
+                dist.init_process_group("nccl", rank=0, world_size=1, device_id=device)
+                env.own_group = dist
+            xchg = ContextExchange(rows=rows, head_dim=cfg["d"], device=device)
+        elif ctx == "nccl" and world > 1:
+            from proxy_attention_lab_b200.sharding import all_gather_packed
+
+            gathered = torch.empty((world, rows, cfg["d"] + 2), dtype=torch.float32, device=device)
+            packed = torch.empty((rows, cfg["d"] + 2), dtype=torch.float32, device=device)
 
         def decode_call(q, table, lens, nk=None, nv=None):
             nk, nv = (new_k, new_v) if nk is None and append else (nk, nv)
@@ -476,35 +543,35 @@ def main():
                 pal.fill_kv_pages(nk, nv, data["k_pool"], data["v_pool"], table, last_pos, seq_ids)
             if not ctx:
                 return pal.paged_attention_decode(q, data["k_pool"], data["v_pool"], table, lens, partition_pages=pp)
-            m, l, acc = pal.paged_attention_decode_partials(q, data["k_pool"], data["v_pool"], table, lens, partition_pages=pp)
-            if world > 1:
-                m, l, acc = all_gather_partials(m, l, acc)
-            else:
-                m, l, acc = m[None], l[None], acc[None]
-            return pal.lse_combine(m, l, acc, out_dtype=torch.bfloat16)
+            if ctx == "fused":
+                return xchg.decode(q, data["k_pool"], data["v_pool"], table, lens, partition_pages=pp)
+            if world == 1:
+                part = pal.paged_attention_decode_partials(q, data["k_pool"], data["v_pool"], table, lens, partition_pages=pp, packed=True)
+                return pal.lse_combine_packed(part[None], out_dtype=torch.bfloat16, out_shape=(cfg["S"], data["hq"], cfg["d"]))
+            pal.paged_attention_decode_partials(q, data["k_pool"], data["v_pool"], table, lens, partition_pages=pp, packed=True, out=packed)
+            all_gather_packed(packed, out=gathered)
+            return pal.lse_combine_packed(gathered, out_dtype=torch.bfloat16, out_shape=(cfg["S"], data["hq"], cfg["d"]))
 
-        def step():
-            return decode_call(data["q"], data["table"], data["lens"])
-
+        w.step = lambda: decode_call(data["q"], data["table"], data["lens"])
         out_host = torch.empty((cfg["S"], data["hq"], cfg["d"]), dtype=torch.bfloat16).pin_memory()
         e2e_inputs = {"q": data["q_host"], "table": data["table_host"], "lens": data["lens_host"]}
         if append:
             e2e_inputs.update(new_k=new_k_host, new_v=new_v_host)
-        pipe = HostPipeline(e2e_inputs, lambda d: decode_call(d["q"], d["table"], d["lens"], d.get("new_k"), d.get("new_v")), out_host, device)
-
-        h2d = data["q_host"].numel() * 2 + data["table_host"].numel() * 4 + data["lens_host"].numel() * 4
-        d2h = out_host.numel() * 2
-        if append:
-            h2d += 2 * new_k_host.numel() * 2
-        units_per_step, alg_per_step = data["kv_bytes"], data["alg_bytes"]
-        to_value = lambda units, sec: units / sec / 1e9
-        launches_per_step = (3 if ctx else 2) if pp else 1
-        if append == "pair":
-            launches_per_step += 1
-        bound, peak = "hbm", peaks["hbm"]
-        achieved_of = lambda sec: alg_per_step / sec / 1e9
-        roof_unit = "GB/s"
-        l2_note = "KV pool per GPU is larger than L2 (126 MB); every step streams it from HBM"
+        w.pipe = HostPipeline(e2e_inputs, lambda d: decode_call(d["q"], d["table"], d["lens"], d.get("new_k"), d.get("new_v")), out_host, device)
+        w.h2d = data["q_host"].numel() * 2 + data["table_host"].numel() * 4 + data["lens_host"].numel() * 4 + (2 * new_k_host.numel() * 2 if append else 0)
+        w.d2h = out_host.numel() * 2
+        w.units_per_step, w.alg_per_step = data["kv_bytes"], data["alg_bytes"]
+        w.scale = 1e9
+        w.launches_per_step = (2 if data["partition_pages"] else 1) + (1 if append == "pair" else 0)
+        if cfg["partition_pages"] < 0:
+            w.extra_cfg["partition_pages_chosen"] = data["partition_pages"]
+        w.collectives_per_step = 1 if (ctx == "nccl" and world > 1) else 0
+        w.bound, w.peak, w.roof_unit = "hbm", peaks["hbm"], "GB/s"
+        w.l2_note = "KV pool per GPU is larger than L2 (126 MB); every step streams it from HBM"
+        w.tokens = cfg["S"]
+        w.tokens_are_global = w.scaling == "strong"
+        w.data = data
+        w.graph = bool(ctx) and not args.no_cuda_graph
     elif kind == "prefill":
         seqs = None
         if world > 1:
@@ -514,8 +581,8 @@ def main():
             n_all = make_lengths(5, cfg["S"], cfg["nlo"], cfg["n"]).tolist() if "nlo" in cfg else [cfg["n"]] * cfg["S"]
             work = [n * int(h) + n * (n + 1) // 2 for n, h in zip(n_all, hist_all)]
             seqs = partition_sequences(work, world)[rank] or [rank % cfg["S"]]
-            scaling = "strong"
-            extra_cfg["parallelism"] = f"sequence sharded x{world}, no collective"
+            w.scaling = "strong"
+            w.extra_cfg["parallelism"] = f"sequence sharded x{world} (balanced by attention work), no collective"
         data = build_prefill(cfg, device, seed=0, seqs=seqs)
 
         def prefill_call(q, k, v, table, hist, cu=None):
@@ -524,129 +591,247 @@ def main():
             return pal.paged_attention_prefill_ragged(q, k, v, data["k_pool"], data["v_pool"], table, hist, cu,
                                                       max_new_tokens=data["max_new"], impl=args.prefill_impl)
 
-        def step():
-            return prefill_call(data["q"], data["k"], data["v"], data["table"], data["hist"], data.get("cu"))
-
+        w.step = lambda: prefill_call(data["q"], data["k"], data["v"], data["table"], data["hist"], data.get("cu"))
         host = {k: data[k].cpu().pin_memory() for k in ("q", "k", "v", "table", "hist") + (("cu",) if "cu" in data else ())}
         out_host = torch.empty((data["tokens"] * cfg["hq"], cfg["d"]), dtype=torch.bfloat16).pin_memory()
-        pipe = HostPipeline(host, lambda d: prefill_call(d["q"], d["k"], d["v"], d["table"], d["hist"], d.get("cu")), out_host, device)
-
-        h2d = sum(t.numel() * t.element_size() for t in host.values())
-        d2h = out_host.numel() * 2
-        units_per_step = alg_per_step = data["flops"]
-        to_value = lambda units, sec: units / sec / 1e12
-        launches_per_step = 1
-        bound, peak = "tensor", peaks["tensor_sustained"] if args.steps >= 200 else peaks["tensor"]
-        achieved_of = lambda sec: alg_per_step / sec / 1e12
-        roof_unit = "TFLOP/s"
-        l2_note = "L2 flushed by design of the workload: Q/K/V/out of a step total ~0.4 GB (> 126 MB L2)"
+        w.pipe = HostPipeline(host, lambda d: prefill_call(d["q"], d["k"], d["v"], d["table"], d["hist"], d.get("cu")), out_host, device)
+        w.h2d = sum(t.numel() * t.element_size() for t in host.values())
+        w.d2h = out_host.numel() * 2
+        w.units_per_step = w.alg_per_step = data["flops"]
+        w.scale = 1e12
+        w.launches_per_step, w.collectives_per_step = 1, 0
+        w.bound, w.roof_unit = "tensor", "TFLOP/s"
+        w.peak = None  # chosen by the length of the timed block (burst or sustained figure)
+        w.l2_note = "Q/K/V/out of a step total ~0.4 GB (> 126 MB L2)"
+        w.tokens = data["tokens"]
+        w.tokens_are_global = False
+        w.data = data
+        w.graph = False
     else:
         data = build_fill(cfg, device, seed=rank)
+        w.step = lambda: pal.fill_kv_pages(data["keys"], data["vals"], data["k_pool"], data["v_pool"], data["slots"])
+        w.pipe = HostPipeline({"keys": data["keys_host"], "vals": data["vals_host"], "slots": data["slots_host"]},
+                              lambda d: pal.fill_kv_pages(d["keys"], d["vals"], data["k_pool"], data["v_pool"], d["slots"]) and None, None, device)
+        w.h2d = data["keys_host"].numel() * 4 + data["slots_host"].numel() * 8
+        w.d2h = 0
+        w.units_per_step = w.alg_per_step = data["alg_bytes"]
+        w.scale = 1e9
+        w.launches_per_step, w.collectives_per_step = 1, 0
+        w.bound, w.peak, w.roof_unit = "hbm", peaks["hbm"], "GB/s"
+        w.l2_note = "source tokens plus touched sectors exceed L2 (126 MB)"
+        w.tokens = data["tokens"]
+        w.tokens_are_global = False
+        w.data = data
+        w.graph = False
+        if world > 1:
+            w.extra_cfg["parallelism"] = f"token sharded x{world} (each GPU its own tokens and pool), no collective"
+    return w
 
-        def step():
-            return pal.fill_kv_pages(data["keys"], data["vals"], data["k_pool"], data["v_pool"], data["slots"])
 
-        pipe = HostPipeline({"keys": data["keys_host"], "vals": data["vals_host"], "slots": data["slots_host"]},
-                            lambda d: pal.fill_kv_pages(d["keys"], d["vals"], data["k_pool"], data["v_pool"], d["slots"]) and None, None, device)
-
-        h2d = data["keys_host"].numel() * 4 + data["slots_host"].numel() * 8
-        d2h = 0
-        units_per_step = alg_per_step = data["alg_bytes"]
-        to_value = lambda units, sec: units / sec / 1e9
-        launches_per_step = 1
-        bound, peak = "hbm", peaks["hbm"]
-        achieved_of = lambda sec: alg_per_step / sec / 1e9
-        roof_unit = "GB/s"
-        l2_note = "source tokens plus touched sectors exceed L2 (126 MB)"
-
-    def timed(fn, steps, warmup, sample_clocks, drain=None):
-        for _ in range(warmup):
-            fn()
-        if drain:
-            drain()
-        barrier()
+def timed_blocks(env, fn, steps, warmup, blocks, drain=None, sampler=None):
+    """`blocks` timed blocks of exactly `steps` calls each, every block bracketed by barrier + synchronize and timed with
+    CUDA events on the launching stream; per block the slowest rank's time.  Returns seconds per block."""
+    for _ in range(warmup):
+        fn()
+    if drain:
+        drain()
+    env.barrier()
+    if sampler:
+        sampler.__enter__()
+    out = []
+    for _ in range(blocks):
+        env.barrier()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        sampler = ClockSampler(local_rank) if sample_clocks else None
-        if sampler:
-            sampler.__enter__()
         e0.record()
         for _ in range(steps):
             fn()
         if drain:
             drain()  # the end event waits for the copy streams as well
         e1.record()
-        barrier()
-        if sampler:
-            sampler.__exit__()
-        ms = e0.elapsed_time(e1)
-        if world > 1:
-            t = torch.tensor([ms], device=device, dtype=torch.float64)
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
-            ms = float(t.item())
-        return ms / 1e3, sampler
+        env.barrier()
+        out.append(env.max_over_ranks(e0.elapsed_time(e1)) / 1e3)
+    if sampler:
+        sampler.__exit__()
+    return out
 
-    # The context-sharded step is nine small launches and an NCCL call around 85 us of attention per GPU at 8 GPUs: the
-    # host cannot enqueue it as fast as the GPU runs it.  It is replayed from a CUDA graph, as a serving loop would do
-    # (every rank captures the same sequence; if the capture is refused the step stays eager and the line says so).
-    graph = graph_out = None
-    if cfg.get("ctx_sharded") and not args.no_cuda_graph:
+
+def median(xs):
+    s = sorted(xs)
+    return s[len(s) // 2] if len(s) % 2 else 0.5 * (s[len(s) // 2 - 1] + s[len(s) // 2])
+
+
+def measure(w, env, peaks, steps, warmup, blocks, e2e=True):
+    """Time a prepared workload; returns the record that goes into the JSON line (identical on every rank)."""
+    step = w.step
+    graph_note = None
+    keep = None
+    if w.graph:
+        # The context-sharded step is a handful of small launches (and a collective) around tens of microseconds of
+        # attention per GPU: it is replayed from a CUDA graph, as a serving loop would do.  If the capture is refused the
+        # step stays eager and the record says so.
         try:
             for _ in range(3):
                 step()
-            barrier()
-            graph = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(graph):
-                graph_out = step()  # noqa: F841  (kept alive: the graph writes into it)
-            step = graph.replay
-            extra_cfg["cuda_graph"] = True
-        except Exception as exc:  # capture of the collective refused: fall back, visibly
-            extra_cfg["cuda_graph"] = f"capture failed ({type(exc).__name__}); eager"
-    sec, sampler = timed(step, args.steps, args.warmup, True)
-    e2e_steps = max(3, min(args.steps, 200))
-    sec_e2e, _ = timed(pipe.step, e2e_steps, 3, False, drain=pipe.drain)
+            env.barrier()
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                keep = step()  # kept alive: the graph writes into it
+            step, graph_note = g.replay, True
+            w.held_graph = (g, keep)
+        except Exception as exc:  # noqa: BLE001
+            graph_note = f"capture failed ({type(exc).__name__}: {str(exc)[:80]}); eager"
+    sampler = ClockSampler(env.local_rank)
+    secs = timed_blocks(env, step, steps, warmup, blocks, sampler=sampler)
+    sec_med, sec_min = median(secs), min(secs)
+    units = w.units_per_step if w.units_are_global else env.sum_over_ranks(float(w.units_per_step))
+    tokens = w.tokens if (w.tokens_are_global or env.world == 1) else env.sum_over_ranks(float(w.tokens))
+    per_step = sec_med / steps
+    rec = {
+        "metric": w.metric, "unit": w.unit, "workload": w.cfg["desc"], "scaling": w.scaling,
+        "value": units * steps / sec_med / w.scale, "value_best_block": units * steps / sec_min / w.scale,
+        "ms_per_step": per_step * 1e3, "blocks": blocks, "steps_per_block": steps, "tokens_per_s": tokens / per_step,
+        "gpu_launches_per_step": w.launches_per_step, "collectives_per_step": w.collectives_per_step,
+    }
+    rec.update(w.extra_cfg)
+    if graph_note is not None:
+        rec["cuda_graph"] = graph_note
+    peak = w.peak
+    if peak is None:  # tensor-bound: a block shorter than ~1 s runs at burst clocks, a longer one under the power cap
+        peak, rec["peak_kind"] = (peaks["tensor_sustained"], "sustained") if sec_med >= 1.0 else (peaks["tensor"], "burst")
+    achieved = w.alg_per_step / per_step / w.scale  # this rank's algorithmic bytes / flops over the step time
+    rec["roofline"] = {"bound": w.bound, "achieved": achieved, "peak": peak, "unit": w.roof_unit, "frac": achieved / peak,
+                       "peak_source": peaks["source"], "per": "GPU (rank 0's algorithmic work / step time of the slowest rank)"}
+    rec["clocks"] = sampler.summary()
+    rec["l2"] = w.l2_note
+    if e2e and w.pipe is not None:
+        e2e_steps = max(3, min(steps, 200))
+        e2e_blocks = max(3, min(blocks, 5))
+        secs_e = timed_blocks(env, w.pipe.step, e2e_steps, 3, e2e_blocks, drain=w.pipe.drain)
+        rec["e2e"] = {"value": units * e2e_steps / median(secs_e) / w.scale, "unit": w.unit, "h2d_bytes_per_step": int(w.h2d),
+                      "d2h_bytes_per_step": int(w.d2h), "steps": e2e_steps, "blocks": e2e_blocks,
+                      "overlap": "copies on their own streams, two sets of device buffers"}
+    return rec
 
-    total_units, total_tokens = units_per_step, data["tokens"]
-    if world > 1:
-        kv_head_sharded = args.workload in ("decode_70b", "decode_70b_ctx")
-        t = torch.tensor([float(units_per_step), 0.0 if kv_head_sharded else float(data["tokens"])], device=device, dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.SUM)
-        total_units = float(t[0].item())
-        total_tokens = data["tokens"] if kv_head_sharded else float(t[1].item())
-    per_step = sec / args.steps
-    value = to_value(total_units * args.steps, sec)
-    e2e_value = to_value(total_units * e2e_steps, sec_e2e)
 
-    if rank == 0:
-        achieved = achieved_of(per_step)
-        # DRAM bytes per launch from one `ncu --set full` capture of the same workload (see profiles/)
-        # fill_append: 0.904 x the algorithmic bytes, from the capture of the reduced case (traffic grows with the tokens)
-        traffic = {"decode_8b": 1.3866e9, "decode_8b_append": 1.3889e9,
-                   "fill_append": 0.904 * alg_per_step}.get(args.workload) if world == 1 else None
-        line = {
-            "metric": metric, "value": value, "unit": unit, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
-            "ms_per_step": per_step * 1e3, "higher_is_better": True, "scaling": scaling, "vs_baseline": None,
-            "dtype": "bf16 (f32 accumulate)", "data": "synthetic",
-            "config": {"workload": cfg["desc"], "l2": l2_note, **extra_cfg},
-            "tokens_per_s": total_tokens / per_step,
-            "e2e": {"value": e2e_value, "unit": unit, "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h), "steps": e2e_steps,
-                    "overlap": "copies on their own streams, two sets of device buffers"},
-            "gpu_launches": launches_per_step * args.steps,
-            "clocks": sampler.summary() if sampler else None,
-            "roofline": {"bound": bound, "achieved": achieved, "peak": peak, "unit": roof_unit, "frac": achieved / peak, "traffic": traffic,
-                         "peak_source": peaks["source"], "kernel": "rank 0 per-step time over the timed region (CUDA events)"},
-        }
-        if world == 1 and not args.no_cpu_baseline:
-            cores = os.cpu_count() or 1
-            torch.set_num_threads(cores)
-            v, what = cpu_measure(cfg, 12.0)
-            line["cpu_baseline"] = {"value": v, "unit": unit, "cores": torch.get_num_threads(), "kind": "port", "sample": what}
+# DRAM bytes per launch from `ncu --set full` captures of the same workloads (summaries under profiles/), not measured
+# in this run; fill_append is 0.904 x its algorithmic bytes (captured on the reduced case; the traffic grows with the tokens).
+PROFILED_TRAFFIC = {"decode_8b": 1.3866e9, "decode_8b_append": 1.3889e9}
+
+EXTRA_SINGLE = ["prefill_8b", "decode_70b", "decode_70b_auto", "fill", "fill_append"]
+EXTRA_MULTI = ["decode_70b", "decode_70b_auto", "decode_70b_ctx", "decode_70b_ctx_fused", "prefill_8b"]
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=500)
+    ap.add_argument("--warmup", type=int, default=10)
+    ap.add_argument("--blocks", type=int, default=10, help="timed blocks of --steps steps each; the median block is reported")
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="decode_8b", choices=sorted(WORKLOADS), help="the headline workload")
+    ap.add_argument("--workloads", default="all", help="extra records in the same line: all | none | comma-separated names")
+    ap.add_argument("--prefill-impl", default="auto")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-cuda-graph", action="store_true", help="context-sharded workloads: enqueue every step from the host")
+    args = ap.parse_args()
+    cfg = WORKLOADS[args.workload]
+    env = Env()
+    if args.impl == "reference":
+        run_reference(args, cfg, env.rank)
+        return
+    args.warmup = max(args.warmup, 3)
+    args.blocks = max(args.blocks, 1)
+
+    import proxy_attention_lab_b200 as pal  # raises if the CUDA library is missing: no fallback
+
+    if not torch.cuda.is_available():
+        raise RuntimeError("bench.py needs a CUDA device; there is no CPU path")
+    env.init()
+    peaks = measured_peaks()
+
+    head = prepare(args.workload, env, pal, peaks, args)
+    rec = measure(head, env, peaks, args.steps, args.warmup, args.blocks)
+    line = {
+        "metric": rec["metric"], "value": rec["value"], "unit": rec["unit"], "n_gpus": env.world, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": rec["ms_per_step"], "higher_is_better": True, "scaling": rec["scaling"], "vs_baseline": None,
+        "dtype": "bf16 (f32 accumulate)", "data": "synthetic",
+        "config": {"workload": cfg["desc"], **head.extra_cfg},
+        "blocks": args.blocks, "value_best_block": rec["value_best_block"], "timing": "median of the timed blocks; each block is exactly `steps` steps",
+        "l2": rec["l2"], "tokens_per_s": rec["tokens_per_s"], "e2e": rec.get("e2e"),
+        "gpu_launches": head.launches_per_step * args.steps * args.blocks,
+        "clocks": rec["clocks"], "roofline": dict(rec["roofline"]),
+    }
+    if "cuda_graph" in rec:
+        line["cuda_graph"] = rec["cuda_graph"]
+    traffic = PROFILED_TRAFFIC.get(args.workload) if env.world == 1 else None
+    if args.workload == "fill_append" and env.world == 1:
+        traffic = 0.904 * head.alg_per_step
+    line["roofline"]["traffic"] = traffic
+    line["roofline"]["traffic_source"] = "ncu capture of this workload (summary committed with the sources), not measured in this run" if traffic else None
+    if env.world == 1 and not args.no_cpu_baseline and env.rank == 0:
+        cores = os.cpu_count() or 1
+        torch.set_num_threads(cores)
+        v, what = cpu_measure(cfg, 12.0, data=head.data if head.kind in ("decode", "prefill") else None)
+        line["cpu_baseline"] = {"value": v, "unit": rec["unit"], "cores": torch.get_num_threads(), "kind": "port", "sample": what}
+    head_data_kept = head  # noqa: F841  (its tensors stay resident; the extra workloads are sized to fit beside them)
+
+    # ---- the other parts of the metric, one record each ----
+    names = []
+    if args.workloads == "all":
+        names = [n for n in (EXTRA_SINGLE if env.world == 1 else EXTRA_MULTI) if n != args.workload]
+    elif args.workloads != "none":
+        names = [n for n in args.workloads.split(",") if n]
+    records = {}
+    # shorter blocks for the extras: they only have to carry two digits
+    x_steps, x_blocks = max(5, min(args.steps, 50)), max(3, min(args.blocks, 10))
+    for name in names:
+        if name not in WORKLOADS:
+            records[name] = {"unavailable": "unknown workload"}
+            continue
+        wcfg = WORKLOADS[name]
+        steps_n = x_steps if wcfg["kind"] != "prefill" else max(5, min(args.steps, 20))
+        w = None
+        try:
+            if wcfg.get("ctx") == "nccl" and env.world == 1:
+                continue  # on one GPU this is decode_70b
+            if wcfg["kind"] == "decode" and env.world > 1 and wcfg["hkv"] % env.world and not wcfg.get("ctx"):
+                records[name] = {"unavailable": f"{wcfg['hkv']} kv heads do not divide over {env.world} GPUs"}
+                continue
+            w = prepare(name, env, pal, peaks, args)
+            r = measure(w, env, peaks, steps_n, max(3, min(args.warmup, 5)), x_blocks)
+            if env.world > 1 and w.scaling == "strong":
+                # the same problem on ONE GPU, run by every rank at the same time: the N = 1 figure of this very run
+                base_name = "decode_70b" if wcfg["kind"] == "decode" else name
+                solo = Env.__new__(Env)
+                solo.__dict__.update(rank=0, world=1, local_rank=env.local_rank, device=env.device, dist=None)
+                del w
+                w = None
+                torch.cuda.empty_cache()
+                w1 = prepare(base_name, solo, pal, peaks, args, force_single=True)
+                secs = timed_blocks(env, w1.step, steps_n, 3, x_blocks)  # env: barriers keep the ranks in step, max over ranks
+                n1 = w1.units_per_step * steps_n / median(secs) / w1.scale
+                r["n1_value_same_run"] = n1
+                r["speedup_vs_n1"] = r["value"] / n1
+                r["efficiency_vs_n1"] = r["value"] / n1 / env.world
+                del w1
+            records[name] = r
+        except Exception as exc:  # noqa: BLE001  (one record failing must not take the headline with it)
+            records[name] = {"unavailable": f"{type(exc).__name__}: {str(exc)[:200]}"}
+        finally:
+            w = None
+            torch.cuda.empty_cache()
+    if names:
+        line["workloads"] = records
+    if env.rank == 0:
         print(json.dumps(line), flush=True)
-    if world > 1:
-        dist.barrier()
-        # a captured graph holds the collective's communicator: release it before the process group goes away
-        step = pipe = graph = graph_out = None  # noqa: F841
+    if env.dist is not None or getattr(env, "own_group", None) is not None:
+        d = env.dist or env.own_group
+        if env.dist is not None:
+            env.dist.barrier()
+        # captured graphs hold the collective's communicator: release them before the process group goes away
+        head = head_data_kept = None  # noqa: F841
         torch.cuda.synchronize()
-        dist.destroy_process_group()
+        d.destroy_process_group()
 
 
 if __name__ == "__main__":

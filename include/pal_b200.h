@@ -122,6 +122,15 @@ int pal_fill_kv_pages_slots(const void* new_keys, const void* new_values, void* 
 size_t pal_decode_workspace_bytes(int num_seqs, int num_q_heads, int num_kv_heads, int head_dim,
                                   int tokens_per_page, int max_pages_per_seq, int partition_pages);
 
+/* The partition size PAL_DECODE_AUTO resolves to for this problem: 0 (single pass) when the batch alone gives
+ * every SM a couple of (sequence, kv head) work items, otherwise the number of pages per partition that makes
+ * the work items fill whole waves of the resident CTAs (two per SM) at the least modelled time - streaming time
+ * of a partition plus a fixed cost per work item, times the number of waves - and never below 16 pages.  The
+ * reference switches to two passes by page-table width alone, with fixed 512-token chunks
+ * (src/pal_core/src/paged_attention_decode_primitive.cpp:100-102). */
+int pal_decode_auto_partition_pages(int num_seqs, int num_q_heads, int num_kv_heads, int head_dim,
+                                    int tokens_per_page, int max_pages_per_seq);
+
 /* Replaces PagedAttentionDecodePrimitive::eval_gpu and its two kernels
  * (src/pal_core/src/paged_attention_decode_primitive.cpp:71-266,
  *  src/pal_core/kernels/paged_attention/decode/paged_attention_decode.h.metal:29-412,
@@ -213,6 +222,31 @@ int pal_lse_combine(const float* m, const float* l, const float* acc, void* out,
  * of pal_paged_attention_decode_partials_packed produces), without unpacking. */
 int pal_lse_combine_packed(const float* packed, void* out, int num_parts, int64_t rows, int head_dim,
                            int dtype, void* stream);
+
+/* ---- context-sharded decode across GPUs --------------------------------------------------- */
+/* For contexts so long that every GPU holds a slice of every sequence (page_table / sequence_lengths describe
+ * this GPU's slice; a rank without tokens of a sequence passes length 0).  One call per GPU and step: the split-KV
+ * pass over the local slice, then ONE kernel that merges the local partitions, stores the merged (acc, m, l) triple
+ * of every row into every rank's exchange buffer with plain peer stores over NVLink, raises a flag, waits (bounded)
+ * for the other ranks' triples and merges them into out [S, Hq, D] - every rank ends up with the full result.
+ * No counterpart in the reference (single GPU).  The alternative without peer memory is
+ * pal_paged_attention_decode_partials_packed + an all-gather (NCCL) + pal_lse_combine_packed.
+ *
+ * peer_bases: host array of world_size device addresses - rank r's exchange buffer as mapped into THIS process
+ * (peer_bases[rank] is this GPU's own).  Each buffer has pal_exchange_bytes(world_size, rows_capacity, head_dim)
+ * bytes, 256-byte aligned, peer-accessible, zeroed once on every rank before the first step (with a barrier
+ * between the zeroing and the first call); rows_capacity >= S * Hq.  How the buffers are shared (CUDA IPC, a
+ * symmetric-memory allocator, cuMem handles) is the caller's business.  All ranks must call once per step, in the
+ * same order; steps may be captured in a CUDA graph (the step number lives in the buffer).  A wait that expires
+ * leaves PAL_ERR_TIMEOUT in the workspace status word and the exchange buffers unusable until zeroed again. */
+size_t pal_exchange_bytes(int world_size, int64_t rows_capacity, int head_dim);
+int pal_paged_attention_decode_ctx_exchange(const void* queries, const void* k_pool, const void* v_pool,
+                                            const void* page_table, const int32_t* sequence_lengths, void* out,
+                                            int num_seqs, int num_q_heads, int num_kv_heads, int head_dim,
+                                            int tokens_per_page, int64_t num_pages, int max_pages_per_seq,
+                                            float scale, int dtype, int partition_pages, void* workspace,
+                                            size_t workspace_bytes, const void* const* peer_bases,
+                                            int world_size, int rank, int64_t rows_capacity, void* stream);
 
 /* ---- paged_attention_prefill -------------------------------------------------------------- */
 /* The prefill kernels need the 256-byte workspace header only: this returns 256 for every problem (the

@@ -39,6 +39,7 @@ SIGNATURES = {
     "pal_fill_kv_pages": (c_int, [_P, _P, _P, _P, _P, _P, _P, c_int64, c_int, c_int, c_int, c_int, c_int64, c_int, c_int, _P]),
     "pal_fill_kv_pages_slots": (c_int, [_P, _P, _P, _P, _P, c_int64, c_int, c_int, c_int, c_int64, c_int, _P]),
     "pal_decode_workspace_bytes": (c_size_t, [c_int, c_int, c_int, c_int, c_int, c_int, c_int]),
+    "pal_decode_auto_partition_pages": (c_int, [c_int, c_int, c_int, c_int, c_int, c_int]),
     "pal_paged_attention_decode": (
         c_int,
         [_P, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int64, c_int, c_float, c_int, c_int, _P, c_size_t, _P],
@@ -68,6 +69,12 @@ SIGNATURES = {
     "pal_paged_attention_decode_partials_packed": (
         c_int,
         [_P, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int64, c_int, c_float, c_int, c_int, _P, c_size_t, _P],
+    ),
+    "pal_exchange_bytes": (c_size_t, [c_int, c_int64, c_int]),
+    "pal_paged_attention_decode_ctx_exchange": (
+        c_int,
+        [_P, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int64, c_int, c_float, c_int, c_int, _P, c_size_t,
+         ctypes.POINTER(c_void_p), c_int, c_int, c_int64, _P],
     ),
     "pal_lse_combine_packed": (c_int, [_P, _P, c_int, c_int64, c_int, c_int, _P]),
     "pal_workspace_init": (c_int, [_P, c_size_t, _P]),

@@ -205,6 +205,13 @@ size_t pal_decode_workspace_bytes(int num_seqs, int num_q_heads, int num_kv_head
                                 partition_pages);
 }
 
+int pal_decode_auto_partition_pages(int num_seqs, int num_q_heads, int num_kv_heads, int head_dim, int tokens_per_page,
+                                    int max_pages_per_seq) {
+  if (num_seqs <= 0 || num_q_heads <= 0 || num_kv_heads <= 0 || head_dim <= 0 || tokens_per_page <= 0 || max_pages_per_seq <= 0)
+    return 0;
+  return decode_auto_partition_pages(num_seqs, num_q_heads, num_kv_heads, head_dim, tokens_per_page, max_pages_per_seq);
+}
+
 static int decode_common(DecodeArgs& a, void* stream, const char* what) {
   if (!split_dtype(a.dtype, what, &a.dtype, &a.out_f32)) return PAL_ERR_UNSUPPORTED;
   int rc = check_heads(what, a.num_q_heads, a.num_kv_heads, a.head_dim, a.tokens_per_page);
@@ -225,7 +232,7 @@ static int decode_common(DecodeArgs& a, void* stream, const char* what) {
   }
   if (a.partition_pages < 0)
     a.partition_pages =
-        decode_auto_partition_pages(a.num_seqs, a.num_q_heads, a.num_kv_heads, a.max_pages_per_seq);
+        decode_auto_partition_pages(a.num_seqs, a.num_q_heads, a.num_kv_heads, a.head_dim, a.tokens_per_page, a.max_pages_per_seq);
   if (a.max_pages_per_seq == 0) a.partition_pages = (a.m_out || a.packed_out) ? 1 : 0;
   const size_t need = decode_workspace_bytes(a.num_seqs, a.num_q_heads, a.num_kv_heads, a.head_dim,
                                              a.tokens_per_page, a.max_pages_per_seq, a.partition_pages);
@@ -380,6 +387,69 @@ int pal_paged_attention_decode_partials_packed(const void* queries, const void* 
     return PAL_ERR_BAD_ARG;
   }
   return decode_common(a, stream, "paged_attention_decode_partials_packed");
+}
+
+size_t pal_exchange_bytes(int world_size, int64_t rows_capacity, int head_dim) {
+  if (world_size < 1 || rows_capacity < 0 || head_dim <= 0) return 0;
+  return exchange_bytes(world_size, rows_capacity, head_dim);
+}
+
+int pal_paged_attention_decode_ctx_exchange(const void* queries, const void* k_pool, const void* v_pool,
+                                            const void* page_table, const int32_t* sequence_lengths, void* out,
+                                            int num_seqs, int num_q_heads, int num_kv_heads, int head_dim,
+                                            int tokens_per_page, int64_t num_pages, int max_pages_per_seq, float scale,
+                                            int dtype, int partition_pages, void* workspace, size_t workspace_bytes,
+                                            const void* const* peer_bases, int world_size, int rank,
+                                            int64_t rows_capacity, void* stream) {
+  const char* what = "paged_attention_decode_ctx_exchange";
+  DecodeArgs a{};
+  a.queries = queries;
+  a.k_pool = k_pool;
+  a.v_pool = v_pool;
+  a.page_table = static_cast<const uint32_t*>(page_table);
+  a.sequence_lengths = sequence_lengths;
+  a.out = nullptr;
+  a.skip_combine = true;
+  a.num_seqs = num_seqs;
+  a.num_q_heads = num_q_heads;
+  a.num_kv_heads = num_kv_heads;
+  a.head_dim = head_dim;
+  a.tokens_per_page = tokens_per_page;
+  a.num_pages = num_pages;
+  a.max_pages_per_seq = max_pages_per_seq;
+  a.scale = scale;
+  a.dtype = dtype;
+  a.partition_pages = partition_pages;
+  a.workspace = workspace;
+  a.workspace_bytes = workspace_bytes;
+  if (partition_pages <= 0) {
+    set_error("%s: partition_pages must be > 0", what);
+    return PAL_ERR_BAD_ARG;
+  }
+  if (num_seqs <= 0 || !out || !peer_bases) {
+    // every rank has to take part in every step: an empty batch is an error here, not a no-op
+    set_error("%s: num_seqs must be positive and out / peer_bases non-null", what);
+    return PAL_ERR_BAD_ARG;
+  }
+  if (max_pages_per_seq <= 0) {
+    set_error("%s: max_pages_per_seq must be positive (a rank without context passes lengths of 0)", what);
+    return PAL_ERR_BAD_ARG;
+  }
+  int rc = decode_common(a, stream, what);  // split-KV pass over this GPU's slice; a.dtype / a.out_f32 are split there
+  if (rc != PAL_OK) return rc;
+  ExchangeArgs x{};
+  x.in = decode_partials_view(a, &x.num_parts);
+  x.rows = (long long)num_seqs * num_q_heads;
+  x.head_dim = head_dim;
+  x.out = out;
+  x.out_f32 = a.out_f32;
+  x.dtype = a.dtype;
+  x.world_size = world_size;
+  x.rank = rank;
+  x.rows_capacity = rows_capacity;
+  x.peer_bases = peer_bases;
+  x.workspace = workspace;
+  return cuda_rc(launch_exchange_combine(x, (cudaStream_t)stream), what);
 }
 
 static int combine_common(const char* what, const PartialsView& in, void* out, int num_parts, int64_t rows, int head_dim,

@@ -672,26 +672,44 @@ int decode_num_partitions(int max_pages_per_seq, int partition_pages) {
   return n < 1 ? 1 : n;
 }
 
-// Two-pass when the batch alone cannot give every SM a couple of work items; partitions are sized so
-// that roughly four items per SM exist, but never smaller than 16 pages.
-int decode_auto_partition_pages(int num_seqs, int num_q_heads, int num_kv_heads, int max_pages_per_seq) {
+// Two-pass when the batch alone cannot give every SM a couple of work items.  The number of partitions per sequence is
+// then the one with the least modelled step time: the work items run in waves over the resident CTAs (two per SM), a wave
+// lasts as long as one item - its pages at one CTA's share of the memory bandwidth plus a fixed cost per item (scheduling,
+// query load, the merge of the four warps, the partial write; about 3 us measured) - and partial waves cost a whole one.
+// Measured on B200 with 8 sequences x 131072 tokens: one kv head per GPU runs 256-page partitions (256 items, one per CTA
+// with 40 CTAs idle) in 101 us, and 128-page partitions (512 items, 1.7 waves) in 126 us.
+int decode_auto_partition_pages(int num_seqs, int num_q_heads, int num_kv_heads, int head_dim, int tokens_per_page,
+                                int max_pages_per_seq) {
   const int group = num_q_heads / num_kv_heads;
-  const int hpi = group > kHeadsPerItem ? 2 * kHeadsPerItem : kHeadsPerItem;
-  const long long items = (long long)num_seqs * num_kv_heads * ((group + hpi - 1) / hpi);
-  const long long want = 148LL * 4;
-  if (items >= 148LL * 2 || max_pages_per_seq <= 32) return 0;
-  long long parts = (want + items - 1) / items;
-  long long pp = (max_pages_per_seq + parts - 1) / parts;
-  if (pp < 16) pp = 16;
-  if (pp >= max_pages_per_seq) return 0;
-  return (int)pp;
+  const int hpi = heads_per_item(group, head_dim);
+  const long long base = (long long)num_seqs * num_kv_heads * ((group + hpi - 1) / hpi);
+  const long long slots = 2LL * cached_sm_count();
+  if (base >= slots || max_pages_per_seq <= 32) return 0;
+  // nanoseconds to stream one page's K and V blocks at 1/slots of ~6.6 TB/s
+  const double page_ns = (double)head_dim * tokens_per_page * 4.0 * (double)slots / 6600.0;
+  const double item_ns = 3000.0;
+  int best_parts = 1;
+  double best = 1e30;
+  const int max_parts = max_pages_per_seq / 16;
+  for (int parts = 1; parts <= max_parts && parts <= 4096; ++parts) {
+    const int pp = (max_pages_per_seq + parts - 1) / parts;
+    const long long items = base * ((max_pages_per_seq + pp - 1) / pp);
+    const long long waves = (items + slots - 1) / slots;
+    const double t = (double)waves * (pp * page_ns + item_ns);
+    if (t < best * 0.999) {  // ties go to fewer, larger partitions
+      best = t;
+      best_parts = parts;
+    }
+    if (items > 64 * slots) break;
+  }
+  const int pp = (max_pages_per_seq + best_parts - 1) / best_parts;
+  return pp >= max_pages_per_seq ? 0 : pp;
 }
 
 size_t decode_workspace_bytes(int num_seqs, int num_q_heads, int num_kv_heads, int head_dim, int tokens_per_page,
                               int max_pages_per_seq, int partition_pages) {
-  (void)tokens_per_page;
   if (partition_pages < 0)
-    partition_pages = decode_auto_partition_pages(num_seqs, num_q_heads, num_kv_heads, max_pages_per_seq);
+    partition_pages = decode_auto_partition_pages(num_seqs, num_q_heads, num_kv_heads, head_dim, tokens_per_page, max_pages_per_seq);
   size_t bytes = sizeof(WorkspaceHeader);
   if (partition_pages > 0) {
     const size_t rows = (size_t)num_seqs * num_q_heads * decode_num_partitions(max_pages_per_seq, partition_pages);
@@ -709,6 +727,22 @@ int launch_lse_combine(const PartialsView& in, void* out, bool out_f32, const Tr
     lse_combine_kernel<__nv_bfloat16><<<(unsigned)rows, 128, 0, stream>>>(in, out, out_f32 ? 1 : 0, triple, num_parts,
                                                                          head_dim);
   return (int)cudaGetLastError();
+}
+
+PartialsView decode_partials_view(const DecodeArgs& a, int* num_parts) {
+  const int parts = decode_num_partitions(a.max_pages_per_seq, a.partition_pages);
+  const size_t rows = (size_t)a.num_seqs * a.num_q_heads * parts;
+  unsigned char* ws = static_cast<unsigned char*>(a.workspace);
+  PartialsView v;
+  v.m = reinterpret_cast<float*>(ws + sizeof(WorkspaceHeader));
+  v.l = reinterpret_cast<float*>(ws + sizeof(WorkspaceHeader) + align256(rows * 4));
+  v.acc = reinterpret_cast<float*>(ws + sizeof(WorkspaceHeader) + 2 * align256(rows * 4));
+  v.part_stride_ml = 1;
+  v.row_stride_ml = parts;
+  v.part_stride_acc = a.head_dim;
+  v.row_stride_acc = (long long)parts * a.head_dim;
+  *num_parts = parts;
+  return v;
 }
 
 int launch_decode(const DecodeArgs& a, cudaStream_t stream) {
@@ -763,7 +797,7 @@ int launch_decode(const DecodeArgs& a, cudaStream_t stream) {
              : (split ? dispatch_shape<__nv_bfloat16, true, 1>(p, a.head_dim, a.tokens_per_page, sms, stream)
                       : dispatch_shape<__nv_bfloat16, false, 1>(p, a.head_dim, a.tokens_per_page, sms, stream));
   if (rc != 0) return rc;
-  if (split) {
+  if (split && !a.skip_combine) {
     const long long out_rows = (long long)a.num_seqs * a.num_q_heads;
     const PartialsView in{p.part_m, p.part_l, p.part_acc, 1, p.num_parts, a.head_dim, (long long)p.num_parts * a.head_dim};
     TripleOut triple;

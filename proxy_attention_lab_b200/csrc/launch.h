@@ -72,6 +72,7 @@ struct DecodeArgs {
   float* l_out;
   float* acc_out;
   float* packed_out = nullptr;  // or the same triple as one [S*Hq, D + 2] buffer: acc, then m, then l
+  bool skip_combine = false;    // two-pass only: leave the per-partition partials in the workspace (see decode_partials_view)
   int num_seqs;
   int num_q_heads;
   int num_kv_heads;
@@ -133,15 +134,36 @@ struct TripleOut {
   float* acc = nullptr;
   long long row_stride_ml = 1, row_stride_acc = 0;
 };
+// The per-partition partials a two-pass launch_decode leaves in `workspace` for this problem, and their count per row.
+PartialsView decode_partials_view(const DecodeArgs& a, int* num_parts);
 int launch_lse_combine(const PartialsView& in, void* out, bool out_f32, const TripleOut& triple, int num_parts,
                        long long rows, int head_dim, int dtype, cudaStream_t stream);
+// Context-sharded decode, second half: merge this GPU's partitions, store the merged triple into every peer's exchange
+// buffer, wait (bounded) for all peers' triples and merge them into `out`.  `peer_bases[r]` is rank r's exchange buffer as
+// mapped into this process (see decode_exchange.cu for its layout).
+struct ExchangeArgs {
+  PartialsView in;
+  int num_parts;
+  long long rows;
+  int head_dim;
+  void* out;
+  bool out_f32;
+  int dtype;
+  int world_size, rank;
+  long long rows_capacity;
+  const void* const* peer_bases;
+  void* workspace;  // its status word receives a timeout
+};
+size_t exchange_bytes(int world_size, long long rows_capacity, int head_dim);
+int launch_exchange_combine(const ExchangeArgs& a, cudaStream_t stream);
 int launch_prefill_mma(const PrefillArgs& a, cudaStream_t stream);
 int launch_prefill_tcgen05(const PrefillArgs& a, cudaStream_t stream);
 
 size_t decode_workspace_bytes(int num_seqs, int num_q_heads, int num_kv_heads, int head_dim, int tokens_per_page,
                               int max_pages_per_seq, int partition_pages);
 int decode_num_partitions(int max_pages_per_seq, int partition_pages);
-int decode_auto_partition_pages(int num_seqs, int num_q_heads, int num_kv_heads, int max_pages_per_seq);
+int decode_auto_partition_pages(int num_seqs, int num_q_heads, int num_kv_heads, int head_dim, int tokens_per_page,
+                                int max_pages_per_seq);
 
 void set_error(const char* fmt, ...);
 // cudaError_t (as int) or negative PAL_ERR_* -> PAL_* return code, with the message set

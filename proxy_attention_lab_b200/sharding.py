@@ -88,3 +88,69 @@ def decode_context_parallel(partials_fn: Callable[[], tuple], combine_fn: Callab
         return combine_fn(all_gather_packed(part, group=group))
     m_all, l_all, acc_all = all_gather_partials(*part, group=group)
     return combine_fn(m_all, l_all, acc_all)
+
+
+class ContextExchange:
+    """Peer-memory exchange for context-sharded decode: the fused alternative to ``all_gather_packed`` + ``lse_combine_packed``.
+
+    Every rank allocates one exchange buffer in symmetric memory (``torch.distributed._symmetric_memory``, which maps each
+    rank's buffer into every process of the group over NVLink), zeroes it, and from then on one call of :meth:`decode` per
+    step runs the split-KV pass over the rank's slice of the context plus ONE kernel that publishes the rank's merged
+    partials to all peers with plain stores, waits (bounded) for theirs and writes the full attention output.  No
+    collective is issued and nothing is copied on the host side of a step.
+
+    ``rows`` is the largest ``num_sequences * num_q_heads`` a step will carry.  All ranks of ``group`` construct the object
+    together and call :meth:`decode` once per step in the same order.  Multicast (NVLS) is not used and is switched off
+    for the allocation.
+    """
+
+    def __init__(self, rows: int, head_dim: int, device, group=None):
+        import ctypes
+        import os
+
+        import torch.distributed._symmetric_memory as symm_mem
+
+        from . import _lib
+
+        self._lib = _lib
+        group = dist.group.WORLD if group is None else group
+        self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
+        self.rows, self.head_dim, self.device = int(rows), int(head_dim), torch.device(device)
+        nbytes = _lib.lib.pal_exchange_bytes(self.world, self.rows, self.head_dim)
+        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")  # plain peer stores only: nothing binds to a multicast object
+        self.buffer = symm_mem.empty(nbytes, dtype=torch.uint8, device=self.device)
+        self.buffer.zero_()
+        self.handle = symm_mem.rendezvous(self.buffer, group.group_name)
+        ptrs = [int(p) for p in self.handle.buffer_ptrs]
+        if len(ptrs) != self.world or any(p == 0 for p in ptrs):
+            raise RuntimeError("symmetric memory did not return a peer mapping for every rank")
+        self._peer_bases = (ctypes.c_void_p * self.world)(*ptrs)
+        torch.cuda.synchronize(self.device)
+        dist.barrier(group)  # every rank's buffer is zero before anyone's first step
+
+    def decode(self, queries, k_cache_pool, v_cache_pool, page_table, sequence_lengths, *, partition_pages: int = 256,
+               scale=None, out_dtype=None, stream=None):
+        """``paged_attention_decode`` over a context that is sliced across the ranks: ``page_table`` / ``sequence_lengths``
+        describe this rank's slice (length 0 where the rank holds nothing of a sequence), ``queries`` are the same on every
+        rank.  Returns the full ``[S, Hq, D]`` result on every rank."""
+        from . import ops
+
+        _lib, lib = self._lib, self._lib.lib
+        S, hq, hkv, d, tpp, num_pages = ops._decode_shapes(queries, k_cache_pool, v_cache_pool, page_table, sequence_lengths)
+        if S * hq > self.rows or d != self.head_dim:
+            raise ValueError(f"this exchange was sized for {self.rows} rows of head_dim {self.head_dim}, got {S * hq} x {d}")
+        if S == 0 or page_table.shape[1] == 0:
+            raise ValueError("every rank takes part in every step: the batch and the page table must not be empty")
+        code, odt = ops._out_code(queries.dtype, out_dtype)
+        with ops._Scope(self.device, stream) as sp:
+            out = torch.empty((S, hq, d), dtype=odt, device=self.device)
+            q = ops._contig(queries)
+            pt = ops._index32("page_table", page_table)
+            lens = ops._index32("sequence_lengths", sequence_lengths)
+            ws = ops._workspace(ops._decode_ws_bytes(S, hq, hkv, d, tpp, pt.shape[1], int(partition_pages)), self.device, sp)
+            rc = lib.pal_paged_attention_decode_ctx_exchange(
+                q.data_ptr(), ops._ptr(k_cache_pool), ops._ptr(v_cache_pool), pt.data_ptr(), lens.data_ptr(), out.data_ptr(), S, hq,
+                hkv, d, tpp, num_pages, pt.shape[1], 0.0 if scale is None else float(scale), code, int(partition_pages),
+                ws.data_ptr(), ws.numel(), self._peer_bases, self.world, self.rank, self.rows, sp)
+            _lib.check(rc)
+        return out

@@ -148,3 +148,84 @@ def test_all_gather_partials_layout():
     res = _run(_gather_shapes)
     assert res[0] == ((2, 3, 4), (2, 3, 4, 8), [0.0, 1.0], [10.0, 11.0], [100.0, 101.0])
     assert res[1] == res[0]
+
+
+def _packed_partials(c, rank, world, q=None, tpp=16):
+    """This rank's packed [rows, D + 2] partials (acc, m, l per row) over its slice of every sequence, from the oracle."""
+    q = c.q if q is None else q
+    rows = []
+    for s in range(len(c.lens)):
+        L = int(c.lens[s])
+        npg = (L + tpp - 1) // tpp
+        sl = context_slice(npg, world, rank)
+        local_len = max(0, min(L, sl.stop * tpp) - sl.start * tpp) if len(sl) else 0
+        table = c.page_table[s:s + 1, sl.start:sl.stop] if len(sl) else torch.zeros((1, 1), dtype=torch.int32)
+        m, l, acc = decode_partials_oracle(q[s:s + 1], c.k_pool, c.v_pool, table, torch.tensor([local_len]), 1 << 30)
+        rows.append(torch.cat([acc[0, :, 0], m[0, :, 0, None], l[0, :, 0, None]], dim=1))
+    return torch.cat(rows).contiguous()
+
+
+def _merge_packed(gathered, shape):
+    d = gathered.shape[-1] - 2
+    m, l, acc = gathered[:, :, d], gathered[:, :, d + 1], gathered[:, :, :d]
+    return lse_combine_oracle(m.permute(1, 0), l.permute(1, 0), acc.permute(1, 0, 2)).reshape(shape)
+
+
+def _context_sharded_packed(rank, world):
+    from proxy_attention_lab_b200.sharding import all_gather_packed
+
+    c = _case()
+    out = decode_context_parallel(lambda: _packed_partials(c, rank, world), lambda g: _merge_packed(g, (len(c.lens), 8, 64)))
+    # the collective writes into a caller-owned buffer when one is given
+    buf = torch.empty((world, out.shape[0] * out.shape[1], 66))
+    assert all_gather_packed(_packed_partials(c, rank, world), out=buf) is buf
+    return out, _merge_packed(buf, (len(c.lens), 8, 64))
+
+
+def test_context_sharding_packed_buffer_goes_through_one_collective():
+    c = _case()
+    ref = decode_oracle(c.q, c.k_pool, c.v_pool, c.page_table, c.lens)
+    res = _run(_context_sharded_packed)
+    for r in range(2):
+        assert torch.allclose(res[r][0], ref, atol=1e-5) and torch.allclose(res[r][1], ref, atol=1e-5)
+
+
+def _exchange_protocol(rank, world):
+    """The fused exchange's protocol with host ranks: every rank stores its packed rows into slot
+    [step & 1][rank] of EVERY rank's gather buffer (point-to-point sends stand for the peer stores), the receiver's
+    flag for that source takes the step number once the rows have landed, and a rank merges a step only when all
+    its flags show it.  Buffers and flags persist across steps; nothing is cleared in between."""
+    c = _case()
+    rows, d = len(c.lens) * 8, 64
+    gather = torch.zeros((2, world, rows, d + 2))
+    flags = [0] * world
+    epoch = 0
+    outs = []
+    for it in range(4):
+        g = torch.Generator().manual_seed(200 + it)
+        q = torch.randn(c.q.shape, generator=g).to(torch.bfloat16)
+        step = epoch + 1
+        slot = step & 1
+        mine = _packed_partials(c, rank, world, q=q)
+        sends = [dist.isend(mine, dst=r) for r in range(world) if r != rank]
+        gather[slot, rank] = mine
+        flags[rank] = step
+        for r in range(world):
+            if r != rank:
+                dist.recv(gather[slot, r], src=r)
+                flags[r] = step
+        for s in sends:
+            s.wait()
+        assert all(f - step >= 0 for f in flags)
+        outs.append((q, _merge_packed(gather[slot], (len(c.lens), 8, d))))
+        epoch = step
+    return outs
+
+
+def test_fused_exchange_protocol_on_host_ranks():
+    c = _case()
+    res = _run(_exchange_protocol)
+    for r in range(2):
+        for q, out in res[r]:
+            ref = decode_oracle(q, c.k_pool, c.v_pool, c.page_table, c.lens)
+            assert torch.allclose(out, ref, atol=1e-5), (out - ref).abs().max()
