@@ -554,16 +554,16 @@ static int prefill_common(const char* what, const void* q_prompt, const void* k_
   a.impl = impl;
   a.workspace = workspace;
   a.workspace_bytes = workspace_bytes;
-  const bool tc_ok = head_dim == 128 && tokens_per_page == 16;
-  if (impl == 2 && !tc_ok) {
-    set_error("%s: the tcgen05 kernel covers head_dim=128, tokens_per_page=16 only", what);
-    return PAL_ERR_UNSUPPORTED;
-  }
-  if (impl < 0 || impl > 2) {
-    set_error("%s: impl must be 0 (auto), 1 (mma.sync) or 2 (tcgen05)", what);
+  const bool tc_ok = prefill_tcgen05_supports(head_dim, tokens_per_page);
+  if (impl < 0 || impl > 3) {
+    set_error("%s: impl must be 0 (auto), 1 (mma.sync), 2 (tcgen05) or 3 (tcgen05, one accumulator tile per CTA)", what);
     return PAL_ERR_BAD_ARG;
   }
-  const bool use_tc = impl == 2 || (impl == 0 && tc_ok && tokens_per_seq >= 64);
+  if (impl >= 2 && !tc_ok) {
+    set_error("%s: the tcgen05 kernel covers head_dim in {64, 128, 256} with tokens_per_page in {16, 32}", what);
+    return PAL_ERR_UNSUPPORTED;
+  }
+  const bool use_tc = impl >= 2 || (impl == 0 && tc_ok && tokens_per_seq >= 64);
   return cuda_rc(use_tc ? launch_prefill_tcgen05(a, (cudaStream_t)stream) : launch_prefill_mma(a, (cudaStream_t)stream),
                  what);
 }

@@ -19,7 +19,8 @@ def run_prefill(pal, case, device, **kw):
 
 
 def supported(impl, d, tpp=16):
-    return impl == "mma" or (d == 128 and tpp == 16)
+    """The tcgen05 kernel covers the head dims that are whole 64-element blocks; the mma.sync kernel every shape."""
+    return impl == "mma" or (d in (64, 128, 256) and tpp in (16, 32))
 
 
 def check(pal, cuda, case, impl):
@@ -35,7 +36,7 @@ def check(pal, cuda, case, impl):
     assert_parity(out, ref, f"{impl}, 16-bit output")
 
 
-IMPLS = ["mma", "tcgen05"]  # tcgen05 covers head_dim 128 / tokens_per_page 16
+IMPLS = ["mma", "tcgen05", "tcgen05_single"]  # tcgen05_single: one accumulator tile per CTA, S double-buffered
 
 
 @pytest.mark.parametrize("impl", IMPLS)
@@ -60,6 +61,19 @@ def test_head_dims_and_page_sizes(pal, cuda, impl, d, tpp):
         pytest.skip("shape outside the tcgen05 kernel")
     case = make_prefill_case(9, [0, 70, 129], 77, 4, 2, d, tpp=tpp, dtype=torch.bfloat16)
     check(pal, cuda, case, impl)
+
+
+@pytest.mark.parametrize("impl", ["tcgen05", "tcgen05_single"])
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("d", [64, 128, 256])
+@pytest.mark.parametrize("tpp", [16, 32])
+def test_tcgen05_shapes_with_long_history_and_several_tiles(pal, cuda, impl, dtype, d, tpp):
+    """Every tcgen05 instantiation over several history tiles (a partial last page, a partial last tile), several query
+    tiles and a poisoned pool; heads paired per kv head (group 2), a lone head per kv head (query tiles paired) and the
+    single-tile form."""
+    for hq, hkv in ((4, 2), (3, 3)):
+        case = make_prefill_case(17 + d + tpp, [700, 0, 131], 300, hq, hkv, d, tpp=tpp, dtype=dtype, poison_unused=True)
+        check(pal, cuda, case, impl)
 
 
 @pytest.mark.parametrize("impl", IMPLS)
@@ -112,7 +126,7 @@ def test_tcgen05_matches_mma(pal, cuda, dtype):
 
 
 def test_tcgen05_unsupported_shape_raises(pal, cuda):
-    case = make_prefill_case(35, [10], 16, 4, 2, 64, dtype=torch.float16)
+    case = make_prefill_case(35, [10], 16, 4, 2, 96, dtype=torch.float16)
     t = to_dev(case, cuda)
     with pytest.raises(RuntimeError):
         pal.paged_attention_prefill(t["q"], t["k_new"], t["v_new"], t["k_pool"], t["v_pool"], t["page_table"], t["hist"], impl="tcgen05")

@@ -9,7 +9,7 @@ from oracle import prefill_ragged_oracle
 pytestmark = pytest.mark.gpu
 
 TOL = 2e-3
-IMPLS = ["mma", "tcgen05"]
+IMPLS = ["mma", "tcgen05", "tcgen05_single"]
 
 
 def make_ragged_case(seed, hist_lens, new_counts, hq, hkv, d, tpp=16, dtype=torch.bfloat16, poison_unused=False):
@@ -46,6 +46,35 @@ def test_mixed_counts_around_tile_edges(pal, cuda, impl, dtype):
     counts = [1, 300, 0, 64, 127, 128, 129, 5, 1, 200]
     hist = [100, 0, 50, 129, 16, 0, 1000, 77, 2048, 255]
     check(pal, cuda, make_ragged_case(11, hist, counts, 8, 2, 128, dtype=dtype), impl)
+
+
+@pytest.mark.parametrize("impl", ["tcgen05", "tcgen05_single"])
+@pytest.mark.parametrize("d,tpp", [(64, 16), (64, 32), (128, 32), (256, 16), (256, 32)])
+def test_ragged_batches_on_the_other_tcgen05_shapes(pal, cuda, impl, d, tpp):
+    counts = [1, 140, 0, 64, 129, 5]
+    hist = [100, 0, 50, 129, 16, 300]
+    check(pal, cuda, make_ragged_case(21, hist, counts, 4, 2, d, tpp=tpp, poison_unused=True), impl)
+
+
+def test_neighbours_values_cannot_leak_into_a_short_sequence(pal, cuda):
+    """The dense V tile of a short sequence also brings in rows of the next sequence; their keys are masked, and their
+    values - here NaN for every sequence but the one under test - must not reach the accumulator either."""
+    counts = [5, 130, 7]
+    c = make_ragged_case(22, [40, 0, 10], counts, 4, 2, 128)
+    ref = prefill_ragged_oracle(c["q"], c["k"], c["v"], c["k_pool"], c["v_pool"], c["table"], c["hist"], c["cu"])
+    cu = c["cu"].tolist()
+    for victim in range(3):
+        poisoned = dict(c)
+        v = c["v"].clone()
+        for s in range(3):
+            if s != victim:
+                v[cu[s]:cu[s + 1]] = float("nan")
+        poisoned["v"] = v
+        for impl in ("mma", "tcgen05", "tcgen05_single"):
+            out = run(pal, cuda, poisoned, impl=impl).reshape(-1, 4, 128)
+            got = out[cu[victim]:cu[victim + 1]]
+            assert torch.isfinite(got.float()).all(), (victim, impl)
+            assert_parity(got, ref.reshape(-1, 4, 128)[cu[victim]:cu[victim + 1]], f"{impl}, sequence {victim}")
 
 
 @pytest.mark.parametrize("impl", IMPLS)
