@@ -122,6 +122,9 @@ struct Mma16816<__half> {
     __half2 h = __floats2half2_rn(lo, hi);
     return *reinterpret_cast<uint32_t*>(&h);
   }
+  __device__ static __forceinline__ float2 unpack(uint32_t v) {
+    return __half22float2(*reinterpret_cast<const __half2*>(&v));
+  }
   static constexpr bool kSplitP = false;
   __device__ static __forceinline__ uint32_t pack_residual(float, float, uint32_t) { return 0u; }
   __device__ static __forceinline__ float to_float(__half v) { return __half2float(v); }
@@ -137,6 +140,9 @@ struct Mma16816<__nv_bfloat16> {
   __device__ static __forceinline__ uint32_t pack(float lo, float hi) {
     __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
     return *reinterpret_cast<uint32_t*>(&h);
+  }
+  __device__ static __forceinline__ float2 unpack(uint32_t v) {
+    return make_float2(__uint_as_float(v << 16), __uint_as_float(v & 0xffff0000u));
   }
   static constexpr bool kSplitP = true;
   // bf16 pair of (lo - bf16(lo), hi - bf16(hi)), given the already packed bf16 pair

@@ -341,6 +341,86 @@ __device__ __forceinline__ void tile_exp_store(uint32_t tS, float scale_log2, fl
   l_run += (acc0.x + acc0.y) + (acc1.x + acc1.y);
 }
 
+// The same for key tiles after the first, in ONE pass over S: the scores are exponentiated against the reference the row
+// already has (the result does not depend on the reference point as long as nothing overflows), and instead of a
+// separate row-maximum pass the row sum of every quarter is checked before its P is stored.  A sum within 2^13 proves
+// that no weight of the quarter exceeds 2^13 (safe in fp16 as well); a larger one means that some score lies more than
+// 2^8 above the reference, the case in which the two-pass form moves the reference too.  Then - rarely - the quarter is
+// redone: the row's reference goes up by the (rounded-up) excess, `fix` rescales what the row has accumulated so far
+// (O, the running sum, the P quarters already stored), and the quarter's weights are computed again.
+constexpr float kQuarterSumLimit = 8192.f;
+#ifndef PAL_PREFILL_ONE_PASS
+#define PAL_PREFILL_ONE_PASS 1
+#endif
+constexpr bool kOnePassSoftmax = PAL_PREFILL_ONE_PASS != 0;
+
+template <typename T, bool PAGED, bool MASK, typename Fix>
+__device__ __forceinline__ bool tile_exp_store_checked(uint32_t tS, float scale_log2, float& m_ref, int rel_limit, float& l_run,
+                                                       Fix&& fix) {
+  using PK = Mma16816<T>;
+  float tile_sum = 0.f;
+  const float2 sc2 = make_float2(scale_log2, scale_log2);
+  float2 nm2 = make_float2(-m_ref, -m_ref);
+  uint32_t cur[32], nxt[32];
+  load_quarter<PAGED>(tS, 0, cur);
+  tmem_wait_ld();
+#pragma unroll
+  for (int u = 0; u < 4; ++u) {
+    if (u < 3) load_quarter<PAGED>(tS, u + 1, nxt);
+    uint32_t hi[16];
+    float qsum;
+#pragma unroll 1
+    for (int attempt = 0;; ++attempt) {
+      float2 acc0 = make_float2(0.f, 0.f), acc1 = make_float2(0.f, 0.f);
+#pragma unroll
+      for (int w = 0; w < 16; ++w) {
+        const int pg = w >> 3, ww = w & 7;
+        const int i0 = PAGED ? (ww < 4 ? 8 * pg + 2 * ww : 16 + 8 * pg + 2 * (ww - 4)) : 2 * w;
+        float2 x = __ffma2_rn(make_float2(__uint_as_float(cur[i0]), __uint_as_float(cur[i0 + 1])), sc2, nm2);
+        if (MASK) {
+          const int c0 = PAGED ? (i0 < 16 ? 16 * u + i0 : 64 + 16 * u + (i0 - 16)) : 32 * u + i0;
+          if (col_key_offset<PAGED>(c0) > rel_limit) x.x = -INFINITY;
+          if (col_key_offset<PAGED>(c0 + 1) > rel_limit) x.y = -INFINITY;
+        }
+        const float2 e = make_float2(fast_exp2(x.x), fast_exp2(x.y));
+        hi[w] = PK::pack(e.x, e.y);
+        if (w & 1)
+          acc1 = __fadd2_rn(acc1, e);
+        else
+          acc0 = __fadd2_rn(acc0, e);
+      }
+      qsum = (acc0.x + acc0.y) + (acc1.x + acc1.y);
+      if (attempt > 0 || !__any_sync(0xffffffffu, !(qsum <= kQuarterSumLimit))) break;
+      // ---- rare: some row of this warp has a score far above its reference (the branch is warp-uniform) ----
+      float xm = -INFINITY;
+#pragma unroll
+      for (int i = 0; i < 32; ++i) {
+        float x = fmaf(__uint_as_float(cur[i]), scale_log2, nm2.x);
+        if (MASK) {
+          const int c = PAGED ? (i < 16 ? 16 * u + i : 64 + 16 * u + (i - 16)) : 32 * u + i;
+          if (col_key_offset<PAGED>(c) > rel_limit) x = -INFINITY;
+        }
+        xm = fmaxf(xm, x);
+      }
+      const float delta = xm > 0.f ? ceilf(xm) : 0.f;  // a whole number: scaling the stored weights by 2^-delta is exact
+      const float f = fast_exp2(-delta);
+      if (!fix(f, u)) return false;
+      tile_sum *= f;
+      m_ref += delta;
+      nm2 = make_float2(-m_ref, -m_ref);
+    }
+    tmem_st16(tS + 16 * u, hi);
+    tile_sum += qsum;
+    if (u < 3) {
+      tmem_wait_ld();
+#pragma unroll
+      for (int i = 0; i < 32; ++i) cur[i] = nxt[i];
+    }
+  }
+  l_run += tile_sum;
+  return true;
+}
+
 template <typename T>
 struct Fmt;
 template <>
@@ -447,9 +527,13 @@ __global__ void __launch_bounds__(64 + 128 * NQ, 1)
         for (int kb = 0; kb < kBlocks; ++kb)
           tma_load_4d(sQ + q * kTileBytes + kb * kBlockBytes, &tm_q, kb * 64, h0 + q * kHeadStep, row0 + t0 + q * kRowStep, tma_seq, q_full);
     }
+    // Key tile j lives in ring stage j % ST; its full / empty barriers are those of index j & 1, used for the
+    // (j >> 1)-th time (two barriers per kind even when the ring has one stage, so that nobody ever waits on a barrier
+    // that may be more than one phase away from the one it names - a parity wait cannot tell phases two apart).
     for (int j = 0; j < num_tiles && ok; ++j) {
       const int st = j % ST;
-      const uint32_t par = ((j / ST) & 1) ^ 1;
+      const int jb = j & 1;
+      const int jr = j - ST;  // the tile whose consumption frees this stage
       const bool paged = j < hist_tiles;
       int npg = 0;
       uint32_t my_pid = 0;
@@ -461,37 +545,37 @@ __global__ void __launch_bounds__(64 + 128 * NQ, 1)
         }
       }
       // ---- K ----
-      if (lane == 0) ok = mbar_wait(&k_empty[st], par, p.status);
+      if (lane == 0 && jr >= 0) ok = mbar_wait(&k_empty[jr & 1], (jr >> 1) & 1, p.status);
       ok = __shfl_sync(0xffffffffu, ok, 0);
       if (!ok) break;
       if (paged) {
         // lane i holds page i's id and issues its copy: the pages of a tile go out in parallel, not one after another
-        if (lane == 0) mbar_arrive_expect_tx(&k_full[st], npg * kPageBytes);
+        if (lane == 0) mbar_arrive_expect_tx(&k_full[jb], npg * kPageBytes);
         __syncwarp();
         if (lane < npg)
           bulk_g2s(sK + st * kTileBytes + lane * kPageBytes,
                    static_cast<const unsigned char*>(p.k_pool) + ((size_t)my_pid * p.num_kv_heads + kvh) * kPageBytes,
-                   kPageBytes, &k_full[st]);
+                   kPageBytes, &k_full[jb]);
       } else if (lane == 0) {
         const int jd = j - hist_tiles;
-        mbar_arrive_expect_tx(&k_full[st], kTileBytes);
+        mbar_arrive_expect_tx(&k_full[jb], kTileBytes);
         for (int kb = 0; kb < kBlocks; ++kb)
-          tma_load_4d(sK + st * kTileBytes + kb * kBlockBytes, &tm_k, kb * 64, kvh, row0 + jd * kTile, tma_seq, &k_full[st]);
+          tma_load_4d(sK + st * kTileBytes + kb * kBlockBytes, &tm_k, kb * 64, kvh, row0 + jd * kTile, tma_seq, &k_full[jb]);
       }
       // ---- V ----
-      if (lane == 0) ok = mbar_wait(&v_empty[st], par, p.status);
+      if (lane == 0 && jr >= 0) ok = mbar_wait(&v_empty[jr & 1], (jr >> 1) & 1, p.status);
       ok = __shfl_sync(0xffffffffu, ok, 0);
       if (!ok) break;
       if (paged) {
-        if (lane == 0) mbar_arrive_expect_tx(&v_full[st], npg * kPageBytes);
+        if (lane == 0) mbar_arrive_expect_tx(&v_full[jb], npg * kPageBytes);
         __syncwarp();
         if (lane < npg)
-          tma_load_3d(sV + st * kTileBytes + lane * kPageBytes, &tm_vpool, 0, 0, (int)(my_pid * p.num_kv_heads + kvh), &v_full[st]);
+          tma_load_3d(sV + st * kTileBytes + lane * kPageBytes, &tm_vpool, 0, 0, (int)(my_pid * p.num_kv_heads + kvh), &v_full[jb]);
       } else if (lane == 0) {
         const int jd = j - hist_tiles;
-        mbar_arrive_expect_tx(&v_full[st], kTileBytes);
+        mbar_arrive_expect_tx(&v_full[jb], kTileBytes);
         for (int nb = 0; nb < kBlocks; ++nb)
-          tma_load_4d(sV + st * kTileBytes + nb * kBlockBytes, &tm_v, nb * 64, kvh, row0 + jd * kTile, tma_seq, &v_full[st]);
+          tma_load_4d(sV + st * kTileBytes + nb * kBlockBytes, &tm_v, nb * 64, kvh, row0 + jd * kTile, tma_seq, &v_full[jb]);
       }
     }
   } else if (warp == 1) {
@@ -581,7 +665,7 @@ __global__ void __launch_bounds__(64 + 128 * NQ, 1)
               tc_mma_ts(d_tmem, a_part + kk * 8, vb + (uint64_t)((kk * 2048) >> 4), idesc_pv_dense, (j > 0 || kk > 0 || part > 0));
           }
         }
-        tc_commit(&o_done[q]);
+        tc_commit(&o_done[SBUF == 2 ? (j & 1) : q]);  // one accumulator tile: the two barriers alternate by key tile
       };
 
       if (ok) ok = wait_all(&k_full[0], 0);
@@ -590,32 +674,30 @@ __global__ void __launch_bounds__(64 + 128 * NQ, 1)
         for (int q = 0; q < NQ; ++q) issue_qk(q, 0);
         if (elect_one()) tc_commit(&k_empty[0]);
       }
+      // (all barrier indices below are key tile & 1, all parities (key tile >> 1) & 1; the ring stage is key tile % ST)
       if (SBUF == 2) {
         // One accumulator tile, two S tiles: QK^T of key tile j + 1 goes into the other S tile before PV of tile j is
         // issued, so it runs while the softmax warps work on tile j.  (The tensor pipe executes in issue order: QK^T(j+1)
         // overwrites the S tile whose P was read by PV(j-1), issued before it.)
         for (int j = 0; j < num_tiles && ok; ++j) {
-          const int st = j % ST;
           if (j + 1 < num_tiles) {
-            const int st1 = (j + 1) % ST;
-            ok = wait_all(&k_full[st1], ((j + 1) / ST) & 1);
+            ok = wait_all(&k_full[(j + 1) & 1], ((j + 1) >> 1) & 1);
             if (!ok) break;
             tc_fence_after();
             issue_qk(0, j + 1);
-            if (elect_one()) tc_commit(&k_empty[st1]);
+            if (elect_one()) tc_commit(&k_empty[(j + 1) & 1]);
           }
-          ok = wait_all(&v_full[st], (j / ST) & 1);
+          ok = wait_all(&v_full[j & 1], (j >> 1) & 1);
           if (ok) ok = wait_all(&p_full[j & 1], (j >> 1) & 1);
           if (!ok) break;
           tc_fence_after();
           issue_pv(0, j);
           __syncwarp();
-          if (elect_one()) tc_commit(&v_empty[st]);
+          if (elect_one()) tc_commit(&v_empty[j & 1]);
         }
       } else {
         for (int j = 0; j < num_tiles && ok; ++j) {
-          const int st = j % ST;
-          ok = wait_all(&v_full[st], (j / ST) & 1);
+          ok = wait_all(&v_full[j & 1], (j >> 1) & 1);
           for (int q = 0; q < NQ && ok; ++q) {
             ok = wait_all(&p_full[q], j & 1);
             if (!ok) break;
@@ -623,16 +705,16 @@ __global__ void __launch_bounds__(64 + 128 * NQ, 1)
             issue_pv(q, j);
             if (j + 1 < num_tiles) {
               if (q == 0) {
-                ok = wait_all(&k_full[(j + 1) % ST], ((j + 1) / ST) & 1);
+                ok = wait_all(&k_full[(j + 1) & 1], ((j + 1) >> 1) & 1);
                 if (!ok) break;
                 tc_fence_after();
               }
               issue_qk(q, j + 1);
-              if (q == NQ - 1 && elect_one()) tc_commit(&k_empty[(j + 1) % ST]);
+              if (q == NQ - 1 && elect_one()) tc_commit(&k_empty[(j + 1) & 1]);
             }
           }
           __syncwarp();
-          if (ok && elect_one()) tc_commit(&v_empty[st]);
+          if (ok && elect_one()) tc_commit(&v_empty[j & 1]);
         }
       }
     }
@@ -648,7 +730,13 @@ __global__ void __launch_bounds__(64 + 128 * NQ, 1)
     const int qi = t0q + row;                   // index of this row's query token in its sequence
     float m_used = -INFINITY, l_run = 0.f;
     bool ok = true;
-
+    // PV of key tile `tile` of this accumulator is complete.  (Valid where it is used: when S of key tile j is ready, PV of
+    // tile j - 2 is complete with S double-buffered, PV of tile j - 1 otherwise, so the barrier named here is at most one
+    // phase behind.  With S double-buffered the two o_done barriers alternate by key tile.)
+    auto wait_pv_done = [&](int tile) {
+      return SBUF == 2 ? mbar_wait(&o_done[tile & 1], (tile >> 1) & 1, p.status) : mbar_wait(&o_done[q], tile & 1, p.status);
+    };
+    auto wait_v_landed = [&](int tile) { return mbar_wait(&v_full[tile & 1], (tile >> 1) & 1, p.status); };
     for (int j = 0; j < num_tiles; ++j) {
       const bool paged = j < hist_tiles;
       const int jd = j - hist_tiles;
@@ -656,7 +744,6 @@ __global__ void __launch_bounds__(64 + 128 * NQ, 1)
       const uint32_t s_par = SBUF == 2 ? ((j >> 1) & 1) : (j & 1);   // parity of this use of the S tile
       const uint32_t tS = tmem_base + lane_addr + si * kTile;
       const int vst = j % ST;
-      const uint32_t v_par = (j / ST) & 1;
       if (!(ok = mbar_wait(&s_full[si], s_par, p.status))) break;
       tc_fence_after();
       // which columns need masking at all (warp-uniform), and up to which key offset this row sees
@@ -664,6 +751,46 @@ __global__ void __launch_bounds__(64 + 128 * NQ, 1)
       const int rel_limit = paged ? (H - 1 - j * kTile) : (min(qi, N - 1) - jd * kTile);
       const bool permuted = C::kPermuted && paged;  // column order of this S tile
 
+      // Key tiles after the first take the one-pass form, provided every row of the warp already has a reference and the
+      // CTA does not carry the rounding residual of P.
+      if (kOnePassSoftmax && j > 0 && !split_p && !__any_sync(0xffffffffu, !(m_used > -INFINITY))) {
+        auto fix = [&](float f, int quarters_stored) {
+          // O must be stable before it is rescaled: PV of the previous key tile has to be complete
+          if (!wait_pv_done(j - 1)) return false;
+          tc_fence_after();
+#pragma unroll
+          for (int c4 = 0; c4 < D / 32; ++c4) {
+            uint32_t v[32];
+            tmem_ld32(tO + c4 * 32, v);
+            tmem_wait_ld();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * f);
+            tmem_st32(tO + c4 * 32, v);
+          }
+          for (int u2 = 0; u2 < quarters_stored; ++u2) {
+            uint32_t pk[16];
+            tmem_ld16(tS + 16 * u2, pk);
+            tmem_wait_ld();
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+              const float2 w2 = Mma16816<T>::unpack(pk[i]);
+              pk[i] = Mma16816<T>::pack(w2.x * f, w2.y * f);
+            }
+            tmem_st16(tS + 16 * u2, pk);
+          }
+          tmem_wait_st();
+          l_run *= f;
+          return true;
+        };
+        if (permuted)
+          ok = need_mask ? tile_exp_store_checked<T, true, true>(tS, p.scale_log2, m_used, rel_limit, l_run, fix)
+                         : tile_exp_store_checked<T, true, false>(tS, p.scale_log2, m_used, rel_limit, l_run, fix);
+        else
+          ok = need_mask ? tile_exp_store_checked<T, false, true>(tS, p.scale_log2, m_used, rel_limit, l_run, fix)
+                         : tile_exp_store_checked<T, false, false>(tS, p.scale_log2, m_used, rel_limit, l_run, fix);
+        if (!ok) break;
+        tmem_wait_st();
+      } else {
       // ---- pass 1: row maximum of the scaled scores ----
       float mx;
       if (permuted)
@@ -676,7 +803,7 @@ __global__ void __launch_bounds__(64 + 128 * NQ, 1)
         m_used = m_new;
       } else if (__any_sync(0xffffffffu, m_new > m_used + kRescaleThreshold)) {
         // O_q must be stable: PV(j-1) of this accumulator has to be complete
-        if (!(ok = mbar_wait(&o_done[q], (j - 1) & 1, p.status))) break;
+        if (!(ok = wait_pv_done(j - 1))) break;
         tc_fence_after();
         const float f = fast_exp2(m_used - m_new);
 #pragma unroll
@@ -712,11 +839,12 @@ __global__ void __launch_bounds__(64 + 128 * NQ, 1)
           tile_exp_store<T, false, false, false>(tS, p.scale_log2, m_ref, rel_limit, l_run);
       }
       tmem_wait_st();
+      }
 
       // The last history tile may hold slots past the history length, and pages that were never
       // loaded: zero those V tokens in shared memory, because 0 * NaN would poison the accumulator.
       if (q == 0 && paged && need_mask) {
-        if (!(ok = mbar_wait(&v_full[vst], v_par, p.status))) break;
+        if (!(ok = wait_v_landed(j))) break;
         unsigned char* vt = sV + vst * kTileBytes;
         constexpr int kRowBytes = TPP * 2;  // one head-dim row of a page: 32 bytes (32-byte swizzle) or 64 (64-byte swizzle)
         for (int dr = row; dr < D; dr += kTile) {
@@ -735,7 +863,7 @@ __global__ void __launch_bounds__(64 + 128 * NQ, 1)
       // In a ragged batch the dense tile that holds a sequence's last new tokens also holds rows of the next sequence.
       // Their keys are masked, but their V rows would still be multiplied by P = 0: zero them (0 * NaN again).
       if (q == 0 && !paged && p.cu_seqlens != nullptr && (jd + 1) * kTile > N) {
-        if (!(ok = mbar_wait(&v_full[vst], v_par, p.status))) break;
+        if (!(ok = wait_v_landed(j))) break;
         if (jd * kTile + row >= N) {
           // dense V tile: [blocks of 64 head-dim elements][128 tokens][128 bytes]; the swizzle permutes within a row
           unsigned char* vt = sV + vst * kTileBytes + row * 128;
@@ -752,7 +880,7 @@ __global__ void __launch_bounds__(64 + 128 * NQ, 1)
     }
 
     // ---- epilogue: O / l -> out[((s*N + qi)*Hq + h0 + q)*D + d] ----
-    if (ok) ok = mbar_wait(&o_done[q], (num_tiles - 1) & 1, p.status);
+    if (ok) ok = wait_pv_done(num_tiles - 1);
     // Full tiles (and partial ones of uniform batches, which the tensor map clips at the sequence's end) leave through
     // shared memory: the tile's Q buffer is no longer read by any MMA, has exactly the size and swizzled layout of the
     // output tile, and TMA stores write it out in whole lines.  A partial tile of a ragged batch would run into the
