@@ -12,9 +12,9 @@
 // two consecutive 128-token query tiles of one head.  Keys arrive in tiles of 128 tokens: first the
 // paged history, then the dense prompt keys up to the diagonal tile.
 //
-//   warp 0        producer: Q / dense K / dense V tiles by TMA (128-byte swizzle); history K pages
-//                 by cp.async.bulk (the pool's native striped block) and history V pages by TMA with the
-//                 32- or 64-byte swizzle (a page row is TPP * 2 bytes); K ring and V ring of kStages each.
+//   warp 0        producer: Q / dense K / dense V tiles by TMA (128-byte swizzle); history K by TMA gather4
+//                 requests, one per (8-element chunk, four pages), each lane issuing its own; history V pages by TMA
+//                 with the 32- or 64-byte swizzle (a page row is TPP * 2 bytes); K ring and V ring of kStages each.
 //   warp 1        issues every tcgen05.mma and tcgen05.commit: the warp stays converged and the thread picked by
 //                 elect.sync issues, which lets the compiler keep descriptors in uniform registers (a branch
 //                 on lane 0 instead costs several hundred cycles of the issuing thread per key tile).
@@ -24,12 +24,15 @@
 //
 // Shared-memory operand layouts and their UMMA descriptors (D = head_dim, B = D / 64 blocks of 64 elements)
 //   Q, dense K   [B k-blocks][128 rows][64 el]  K-major, SWIZZLE_128B, SBO 1024; +32 B per K=16 step
-//   paged K      page p at +D*TPP*2 p, inside a page [D/8 chunks of 8 el][TPP tokens][16 B]: every
-//                (chunk, 8 tokens) is one contiguous 128-byte core matrix => K-major, no swizzle, LBO TPP*16 (next chunk).
-//                TPP = 16: SBO = page size (same slots of the next page); one MMA covers slots 0-7 of the 8 pages
-//                (N = 64), a second one slots 8-15: S columns are a permutation of the tile's tokens, which softmax
-//                undoes when it writes P.  TPP = 32: SBO 128 (the next 8 tokens of the same page), one N = 32 MMA
-//                per page, S columns in token order.
+//   paged K      The pool keeps a page as [D/8 chunks of 8 el][TPP tokens][16 B]; every (chunk, 8 tokens) is one
+//                contiguous 128-byte core matrix.  A page copied whole would put the 8-token groups of a 128-key tile at
+//                two different strides (inside a page, across pages), which one descriptor cannot express: with 16-token
+//                pages that costs two N = 64 MMAs per K step and permuted S columns (measured: 920 against 968
+//                TFLOP/s on the chunked-prefill configuration).  Instead the tile is gathered: viewing the pool as a
+//                2-D tensor of (page, kv head, chunk) rows of TPP*16 bytes, one gather4 request puts the same chunk of
+//                four pages back to back, so the tile lands as [D/8 chunks][128 tokens][16 B]: K-major, no swizzle,
+//                LBO 2048 (next chunk), SBO 128 (next 8 tokens), one N = 128 MMA per K step, S columns in token order,
+//                for either page size.
 //   paged V      page p at +D*TPP*2 p: [D rows][TPP tokens], rows of TPP*2 bytes, SWIZZLE_32B / 64B K-major,
 //                SBO 8 rows; one K = 16 MMA per 16 tokens of a page, N = D.
 //   dense V      [B n-blocks][128 tokens][64 el] MN-major, SWIZZLE_128B, LBO 16384, SBO 1024, N = D.
@@ -48,11 +51,11 @@
 // by more than 2^8 (the result is exact either way: numerator and denominator use the same
 // reference point).  Every wait is bounded; on expiry the CTA records a timeout in the workspace
 // status word, still releases its TMEM and returns.
+#pragma once
+
 #include <cuda.h>
 #include <cudaTypedefs.h>
 #include <math.h>
-
-#pragma once
 
 #include "common.cuh"
 #include "launch.h"
@@ -77,7 +80,7 @@ struct TcCfg {
   static constexpr int kPageBytes = D * TPP * 2;
   static constexpr int kTileBytes = kTile * D * 2;
   static constexpr int kStages = D <= 128 ? 2 : 1;    // K ring and V ring depth (head_dim 256: 64 KB per tile)
-  static constexpr bool kPermuted = TPP == 16;        // history S tiles hold the keys in permuted order
+  static constexpr int kChunkBytes = kTile * 16;      // one 8-element chunk of all 128 tokens of a history K tile
   // TMEM columns
   static constexpr int kSCols = NQ * SBUF * kTile;
   static constexpr int kOBase = kSCols;
@@ -119,6 +122,14 @@ __device__ __forceinline__ void tma_load_3d(void* dst, const CUtensorMap* map, i
       "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];" ::"r"(
           smem_u32(dst)),
       "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2)
+      : "memory");
+}
+// Four rows of a 2-D tensor (row indices r0..r3, starting at column c0) land back to back in shared memory.
+__device__ __forceinline__ void tma_gather4(void* dst, const CUtensorMap* map, int c0, int r0, int r1, int r2, int r3, uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cta.global.tile::gather4.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6, %7}], [%2];" ::"r"(
+          smem_u32(dst)),
+      "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(c0), "r"(r0), "r"(r1), "r"(r2), "r"(r3)
       : "memory");
 }
 __device__ __forceinline__ bool elect_one() {
@@ -213,21 +224,16 @@ __host__ __device__ constexpr uint32_t make_idesc(int n, int a_fmt, int b_fmt, i
 
 
 // ---- softmax building blocks ------------------------------------------------------------------
-// Key offset (relative to the tile's first key) held by column c of an S tile.  With 16-token pages a history
-// tile's columns are permuted (PAGED): 0-63 are slots 0-7 of pages 0-7, 64-127 slots 8-15 of the same pages.
-template <bool PAGED>
-__device__ __forceinline__ constexpr int col_key_offset(int c) {
-  return PAGED ? (((c & 63) >> 3) * 16 + (c & 7) + ((c >> 6) << 3)) : c;
-}
+// Column c of an S tile holds key c of the key tile, for history tiles as well as dense ones.
 __device__ __forceinline__ float max3(float a, float b, float c) {
   float d;
   asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
   return d;
 }
 
-// Row maximum of one thread's 128 raw scores; columns whose key offset exceeds rel_limit are ignored.
+// Row maximum of one thread's 128 raw scores; columns past rel_limit are ignored.
 // Four independent chains, the next 32 columns in flight while the current ones are reduced.
-template <bool PAGED, bool MASK>
+template <bool MASK>
 __device__ __forceinline__ float tile_row_max(uint32_t tS, int rel_limit) {
   float m[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
   uint32_t cur[32], nxt[32];
@@ -242,8 +248,8 @@ __device__ __forceinline__ float tile_row_max(uint32_t tS, int rel_limit) {
       for (int k = 0; k < 4; ++k) {
         float a = __uint_as_float(cur[i + 2 * k]), b = __uint_as_float(cur[i + 2 * k + 1]);
         if (MASK) {
-          if (col_key_offset<PAGED>(c4 * 32 + i + 2 * k) > rel_limit) a = -INFINITY;
-          if (col_key_offset<PAGED>(c4 * 32 + i + 2 * k + 1) > rel_limit) b = -INFINITY;
+          if (c4 * 32 + i + 2 * k > rel_limit) a = -INFINITY;
+          if (c4 * 32 + i + 2 * k + 1 > rel_limit) b = -INFINITY;
         }
         m[k] = max3(m[k], a, b);
       }
@@ -257,51 +263,29 @@ __device__ __forceinline__ float tile_row_max(uint32_t tS, int rel_limit) {
   return fmaxf(fmaxf(m[0], m[1]), fmaxf(m[2], m[3]));
 }
 
-// One quarter of an S row: the 32 scores that become P columns [16u, 16u + 16), in P's key order.
-template <bool PAGED>
-__device__ __forceinline__ void load_quarter(uint32_t tS, int u, uint32_t (&v)[32]) {
-  if (PAGED) {
-    // pages 2u, 2u+1: slots 0-7 at S columns 16u.., slots 8-15 at S columns 64 + 16u..
-    uint32_t a16[16], b16[16];
-    tmem_ld16(tS + 16 * u, a16);
-    tmem_ld16(tS + 64 + 16 * u, b16);
-#pragma unroll
-    for (int i = 0; i < 16; ++i) {
-      v[i] = a16[i];
-      v[16 + i] = b16[i];
-    }
-  } else {
-    tmem_ld32(tS + 32 * u, v);
-  }
-}
-
 // P = exp2(s * scale - m_ref) for one row, written as packed 16-bit pairs over S's first 64 columns,
 // a quarter (32 keys -> 16 columns) at a time so that P never overtakes S columns still to be read,
 // with the next quarter's scores in flight.  SPLIT also writes the rounding residual P - round(P)
 // to columns 64..127 (after the scores living there have been consumed).
-template <typename T, bool PAGED, bool MASK, bool SPLIT>
+template <typename T, bool MASK, bool SPLIT>
 __device__ __forceinline__ void tile_exp_store(uint32_t tS, float scale_log2, float m_ref, int rel_limit, float& l_run) {
   using PK = Mma16816<T>;
   float2 acc0 = make_float2(0.f, 0.f), acc1 = make_float2(0.f, 0.f);
   const float2 sc2 = make_float2(scale_log2, scale_log2), nm2 = make_float2(-m_ref, -m_ref);
   uint32_t cur[32], nxt[32];
   uint32_t lo_hold0[16], lo_hold1[16];
-  load_quarter<PAGED>(tS, 0, cur);
+  tmem_ld32(tS, cur);
   tmem_wait_ld();
 #pragma unroll
   for (int u = 0; u < 4; ++u) {
-    if (u < 3) load_quarter<PAGED>(tS, u + 1, nxt);
+    if (u < 3) tmem_ld32(tS + 32 * (u + 1), nxt);
     uint32_t hi[16], lo[16];
 #pragma unroll
     for (int w = 0; w < 16; ++w) {
-      // indices (into cur) of the two keys that land in P column 16u + w
-      const int pg = w >> 3, ww = w & 7;
-      const int i0 = PAGED ? (ww < 4 ? 8 * pg + 2 * ww : 16 + 8 * pg + 2 * (ww - 4)) : 2 * w;
-      float2 x = __ffma2_rn(make_float2(__uint_as_float(cur[i0]), __uint_as_float(cur[i0 + 1])), sc2, nm2);
+      float2 x = __ffma2_rn(make_float2(__uint_as_float(cur[2 * w]), __uint_as_float(cur[2 * w + 1])), sc2, nm2);
       if (MASK) {
-        const int c0 = PAGED ? (i0 < 16 ? 16 * u + i0 : 64 + 16 * u + (i0 - 16)) : 32 * u + i0;
-        if (col_key_offset<PAGED>(c0) > rel_limit) x.x = -INFINITY;
-        if (col_key_offset<PAGED>(c0 + 1) > rel_limit) x.y = -INFINITY;
+        if (32 * u + 2 * w > rel_limit) x.x = -INFINITY;
+        if (32 * u + 2 * w + 1 > rel_limit) x.y = -INFINITY;
       }
       const float2 e = make_float2(fast_exp2(x.x), fast_exp2(x.y));
       hi[w] = PK::pack(e.x, e.y);
@@ -313,9 +297,7 @@ __device__ __forceinline__ void tile_exp_store(uint32_t tS, float scale_log2, fl
     }
     tmem_st16(tS + 16 * u, hi);
     if (SPLIT) {
-      if (PAGED) {
-        tmem_st16(tS + 64 + 16 * u, lo);  // S columns 64 + 16u.. were consumed in this very quarter
-      } else if (u == 0) {
+      if (u == 0) {
 #pragma unroll
         for (int w = 0; w < 16; ++w) lo_hold0[w] = lo[w];
       } else if (u == 1) {
@@ -341,86 +323,6 @@ __device__ __forceinline__ void tile_exp_store(uint32_t tS, float scale_log2, fl
   l_run += (acc0.x + acc0.y) + (acc1.x + acc1.y);
 }
 
-// The same for key tiles after the first, in ONE pass over S: the scores are exponentiated against the reference the row
-// already has (the result does not depend on the reference point as long as nothing overflows), and instead of a
-// separate row-maximum pass the row sum of every quarter is checked before its P is stored.  A sum within 2^13 proves
-// that no weight of the quarter exceeds 2^13 (safe in fp16 as well); a larger one means that some score lies more than
-// 2^8 above the reference, the case in which the two-pass form moves the reference too.  Then - rarely - the quarter is
-// redone: the row's reference goes up by the (rounded-up) excess, `fix` rescales what the row has accumulated so far
-// (O, the running sum, the P quarters already stored), and the quarter's weights are computed again.
-constexpr float kQuarterSumLimit = 8192.f;
-#ifndef PAL_PREFILL_ONE_PASS
-#define PAL_PREFILL_ONE_PASS 1
-#endif
-constexpr bool kOnePassSoftmax = PAL_PREFILL_ONE_PASS != 0;
-
-template <typename T, bool PAGED, bool MASK, typename Fix>
-__device__ __forceinline__ bool tile_exp_store_checked(uint32_t tS, float scale_log2, float& m_ref, int rel_limit, float& l_run,
-                                                       Fix&& fix) {
-  using PK = Mma16816<T>;
-  float tile_sum = 0.f;
-  const float2 sc2 = make_float2(scale_log2, scale_log2);
-  float2 nm2 = make_float2(-m_ref, -m_ref);
-  uint32_t cur[32], nxt[32];
-  load_quarter<PAGED>(tS, 0, cur);
-  tmem_wait_ld();
-#pragma unroll
-  for (int u = 0; u < 4; ++u) {
-    if (u < 3) load_quarter<PAGED>(tS, u + 1, nxt);
-    uint32_t hi[16];
-    float qsum;
-#pragma unroll 1
-    for (int attempt = 0;; ++attempt) {
-      float2 acc0 = make_float2(0.f, 0.f), acc1 = make_float2(0.f, 0.f);
-#pragma unroll
-      for (int w = 0; w < 16; ++w) {
-        const int pg = w >> 3, ww = w & 7;
-        const int i0 = PAGED ? (ww < 4 ? 8 * pg + 2 * ww : 16 + 8 * pg + 2 * (ww - 4)) : 2 * w;
-        float2 x = __ffma2_rn(make_float2(__uint_as_float(cur[i0]), __uint_as_float(cur[i0 + 1])), sc2, nm2);
-        if (MASK) {
-          const int c0 = PAGED ? (i0 < 16 ? 16 * u + i0 : 64 + 16 * u + (i0 - 16)) : 32 * u + i0;
-          if (col_key_offset<PAGED>(c0) > rel_limit) x.x = -INFINITY;
-          if (col_key_offset<PAGED>(c0 + 1) > rel_limit) x.y = -INFINITY;
-        }
-        const float2 e = make_float2(fast_exp2(x.x), fast_exp2(x.y));
-        hi[w] = PK::pack(e.x, e.y);
-        if (w & 1)
-          acc1 = __fadd2_rn(acc1, e);
-        else
-          acc0 = __fadd2_rn(acc0, e);
-      }
-      qsum = (acc0.x + acc0.y) + (acc1.x + acc1.y);
-      if (attempt > 0 || !__any_sync(0xffffffffu, !(qsum <= kQuarterSumLimit))) break;
-      // ---- rare: some row of this warp has a score far above its reference (the branch is warp-uniform) ----
-      float xm = -INFINITY;
-#pragma unroll
-      for (int i = 0; i < 32; ++i) {
-        float x = fmaf(__uint_as_float(cur[i]), scale_log2, nm2.x);
-        if (MASK) {
-          const int c = PAGED ? (i < 16 ? 16 * u + i : 64 + 16 * u + (i - 16)) : 32 * u + i;
-          if (col_key_offset<PAGED>(c) > rel_limit) x = -INFINITY;
-        }
-        xm = fmaxf(xm, x);
-      }
-      const float delta = xm > 0.f ? ceilf(xm) : 0.f;  // a whole number: scaling the stored weights by 2^-delta is exact
-      const float f = fast_exp2(-delta);
-      if (!fix(f, u)) return false;
-      tile_sum *= f;
-      m_ref += delta;
-      nm2 = make_float2(-m_ref, -m_ref);
-    }
-    tmem_st16(tS + 16 * u, hi);
-    tile_sum += qsum;
-    if (u < 3) {
-      tmem_wait_ld();
-#pragma unroll
-      for (int i = 0; i < 32; ++i) cur[i] = nxt[i];
-    }
-  }
-  l_run += tile_sum;
-  return true;
-}
-
 template <typename T>
 struct Fmt;
 template <>
@@ -439,11 +341,10 @@ template <typename T, int D, int TPP, int NQ, bool PAIR_TILES, int SBUF>
 __global__ void __launch_bounds__(64 + 128 * NQ, 1)
     prefill_tcgen05_kernel(const TcParams p, const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                            const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_vpool,
-                           const __grid_constant__ CUtensorMap tm_out) {
+                           const __grid_constant__ CUtensorMap tm_kpool, const __grid_constant__ CUtensorMap tm_out) {
   using C = TcCfg<D, TPP, NQ, SBUF>;
   constexpr int kBlocks = C::kBlocks, kPagesPerTile = C::kPagesPerTile, kPageBytes = C::kPageBytes, kTileBytes = C::kTileBytes;
   constexpr int ST = C::kStages;
-  constexpr int NS = NQ * SBUF;  // S tiles, each with its own s_full / p_full barrier
   extern __shared__ unsigned char smem_raw[];
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   unsigned char* sQ = smem + C::kQ;
@@ -493,7 +394,9 @@ __global__ void __launch_bounds__(64 + 128 * NQ, 1)
   // 256 visible keys - the first one or two query tiles of sequences with little history, the
   // lightest CTAs of the causal schedule - feed the residual P - bf16(P) through a second set of
   // PV MMAs.
-  const bool split_p = Mma16816<T>::kSplitP && (H + t0 < 256);
+  // A caller that asks for a float32 output asks for the arithmetic error alone to stay within tolerance on every row,
+  // including rows dominated by a single key, where the rounding of P shows undiluted: the residual is then always fed.
+  const bool split_p = Mma16816<T>::kSplitP && (p.out_f32 != 0 || H + t0 < 256);
 
   if (tid == 0) {
     mbar_init(q_full, 1);
@@ -549,13 +452,31 @@ __global__ void __launch_bounds__(64 + 128 * NQ, 1)
       ok = __shfl_sync(0xffffffffu, ok, 0);
       if (!ok) break;
       if (paged) {
-        // lane i holds page i's id and issues its copy: the pages of a tile go out in parallel, not one after another
-        if (lane == 0) mbar_arrive_expect_tx(&k_full[jb], npg * kPageBytes);
+        // The pool keeps a page as [chunk of 8 elements][token][16 B].  For each chunk, one gather4 request brings the
+        // chunk's TPP * 16-byte rows of four pages and puts them back to back: the tile becomes [chunk][128 tokens][16 B],
+        // tokens in order, whatever the page size.  One request per lane at a time; groups of four pages that lie wholly
+        // past the history are not fetched (their S columns are masked), pages past it inside a group repeat page 0.
+        constexpr int kChunks = D / 8, kGroups = kPagesPerTile / 4;     // requests per tile = kChunks * kGroups
+        constexpr int kGroupBytes = 4 * TPP * 16;
+        const int groups_used = (npg + 3) >> 2;
+        if (lane == 0) mbar_arrive_expect_tx(&k_full[jb], kChunks * groups_used * kGroupBytes);
         __syncwarp();
-        if (lane < npg)
-          bulk_g2s(sK + st * kTileBytes + lane * kPageBytes,
-                   static_cast<const unsigned char*>(p.k_pool) + ((size_t)my_pid * p.num_kv_heads + kvh) * kPageBytes,
-                   kPageBytes, &k_full[jb]);
+        const int pid0 = __shfl_sync(0xffffffffu, (int)my_pid, 0);
+#pragma unroll
+        for (int op0 = 0; op0 < kChunks * kGroups; op0 += 32) {
+          const int op = op0 + lane;
+          const int c = op / kGroups, g = op % kGroups;
+          int rows[4];
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const int pg = 4 * g + i;  // page of the tile; every lane takes part in the shuffle
+            const int pid = __shfl_sync(0xffffffffu, (int)my_pid, pg & 31);
+            rows[i] = ((pg < npg ? pid : pid0) * p.num_kv_heads + kvh) * kChunks + c;
+          }
+          if (op < kChunks * kGroups && g < groups_used)
+            tma_gather4(sK + st * kTileBytes + c * C::kChunkBytes + g * kGroupBytes, &tm_kpool, 0, rows[0], rows[1], rows[2], rows[3],
+                        &k_full[jb]);
+        }
       } else if (lane == 0) {
         const int jd = j - hist_tiles;
         mbar_arrive_expect_tx(&k_full[jb], kTileBytes);
@@ -583,8 +504,6 @@ __global__ void __launch_bounds__(64 + 128 * NQ, 1)
     {
       constexpr int F = Fmt<T>::kCode;
       constexpr uint32_t idesc_qk128 = make_idesc(128, F, F, 0);
-      constexpr uint32_t idesc_qk64 = make_idesc(64, F, F, 0);
-      constexpr uint32_t idesc_qk32 = make_idesc(32, F, F, 0);
       constexpr uint32_t idesc_pv_paged = make_idesc(D, F, F, 0);  // A = P (TMEM), B = V K-major, N = head_dim
       constexpr uint32_t idesc_pv_dense = make_idesc(D, F, F, 1);  // B = V MN-major
       const uint32_t sQ_u = smem_u32(sQ), sK_u = smem_u32(sK), sV_u = smem_u32(sV);
@@ -596,8 +515,8 @@ __global__ void __launch_bounds__(64 + 128 * NQ, 1)
 #pragma unroll
       for (int st = 0; st < ST; ++st) {
         k_dense[st] = make_desc(sK_u + st * kTileBytes, 16, 1024, kLayoutSw128);
-        // chunks of 8 elements are TPP * 16 bytes apart; 8-token groups: the next page (TPP = 16) or +128 bytes (TPP = 32)
-        k_hist[st] = make_desc(sK_u + st * kTileBytes, TPP * 16, TPP == 16 ? kPageBytes : 128, kLayoutNone);
+        // gathered history K: chunks of 8 elements are 2048 bytes apart, 8-token core matrices 128 bytes
+        k_hist[st] = make_desc(sK_u + st * kTileBytes, C::kChunkBytes, 128, kLayoutNone);
         v_dense[st] = make_desc(sV_u + st * kTileBytes, kBlockBytes, 1024, kLayoutSw128);
         v_hist[st] = make_desc(sV_u + st * kTileBytes, 16, 8 * TPP * 2, TPP == 16 ? kLayoutSw32 : kLayoutSw64);
       }
@@ -622,15 +541,8 @@ __global__ void __launch_bounds__(64 + 128 * NQ, 1)
 #pragma unroll
           for (int ks = 0; ks < D / 16; ++ks) {
             const uint64_t a = qa + (uint64_t)(((ks >> 2) * kBlockBytes + (ks & 3) * 32) >> 4);
-            if (TPP == 16) {
-#pragma unroll
-              for (int half = 0; half < 2; ++half)
-                tc_mma_ss(d_tmem + half * 64, a, kb + (uint64_t)((half * 128 + ks * 2 * (TPP * 16)) >> 4), idesc_qk64, ks > 0);
-            } else {
-#pragma unroll
-              for (int pg = 0; pg < kPagesPerTile; ++pg)
-                tc_mma_ss(d_tmem + pg * TPP, a, kb + (uint64_t)((pg * kPageBytes + ks * 2 * (TPP * 16)) >> 4), idesc_qk32, ks > 0);
-            }
+            // chunks 2 ks and 2 ks + 1 of all 128 tokens
+            tc_mma_ss(d_tmem, a, kb + (uint64_t)((ks * 2 * C::kChunkBytes) >> 4), idesc_qk128, ks > 0);
           }
         } else {
           const uint64_t kb = pick(k_dense, st);
@@ -749,54 +661,10 @@ __global__ void __launch_bounds__(64 + 128 * NQ, 1)
       // which columns need masking at all (warp-uniform), and up to which key offset this row sees
       const bool need_mask = paged ? ((j + 1) * kTile > H) : (jd >= diag || (jd + 1) * kTile > N);
       const int rel_limit = paged ? (H - 1 - j * kTile) : (min(qi, N - 1) - jd * kTile);
-      const bool permuted = C::kPermuted && paged;  // column order of this S tile
 
-      // Key tiles after the first take the one-pass form, provided every row of the warp already has a reference and the
-      // CTA does not carry the rounding residual of P.
-      if (kOnePassSoftmax && j > 0 && !split_p && !__any_sync(0xffffffffu, !(m_used > -INFINITY))) {
-        auto fix = [&](float f, int quarters_stored) {
-          // O must be stable before it is rescaled: PV of the previous key tile has to be complete
-          if (!wait_pv_done(j - 1)) return false;
-          tc_fence_after();
-#pragma unroll
-          for (int c4 = 0; c4 < D / 32; ++c4) {
-            uint32_t v[32];
-            tmem_ld32(tO + c4 * 32, v);
-            tmem_wait_ld();
-#pragma unroll
-            for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * f);
-            tmem_st32(tO + c4 * 32, v);
-          }
-          for (int u2 = 0; u2 < quarters_stored; ++u2) {
-            uint32_t pk[16];
-            tmem_ld16(tS + 16 * u2, pk);
-            tmem_wait_ld();
-#pragma unroll
-            for (int i = 0; i < 16; ++i) {
-              const float2 w2 = Mma16816<T>::unpack(pk[i]);
-              pk[i] = Mma16816<T>::pack(w2.x * f, w2.y * f);
-            }
-            tmem_st16(tS + 16 * u2, pk);
-          }
-          tmem_wait_st();
-          l_run *= f;
-          return true;
-        };
-        if (permuted)
-          ok = need_mask ? tile_exp_store_checked<T, true, true>(tS, p.scale_log2, m_used, rel_limit, l_run, fix)
-                         : tile_exp_store_checked<T, true, false>(tS, p.scale_log2, m_used, rel_limit, l_run, fix);
-        else
-          ok = need_mask ? tile_exp_store_checked<T, false, true>(tS, p.scale_log2, m_used, rel_limit, l_run, fix)
-                         : tile_exp_store_checked<T, false, false>(tS, p.scale_log2, m_used, rel_limit, l_run, fix);
-        if (!ok) break;
-        tmem_wait_st();
-      } else {
       // ---- pass 1: row maximum of the scaled scores ----
       float mx;
-      if (permuted)
-        mx = need_mask ? tile_row_max<true, true>(tS, rel_limit) : tile_row_max<true, false>(tS, rel_limit);
-      else
-        mx = need_mask ? tile_row_max<false, true>(tS, rel_limit) : tile_row_max<false, false>(tS, rel_limit);
+      mx = need_mask ? tile_row_max<true>(tS, rel_limit) : tile_row_max<false>(tS, rel_limit);
       mx *= p.scale_log2;  // scale > 0, so the maximum commutes with the scaling
       const float m_new = fmaxf(m_used, mx);
       if (j == 0) {
@@ -822,24 +690,13 @@ __global__ void __launch_bounds__(64 + 128 * NQ, 1)
       const float m_ref = m_used > -INFINITY ? m_used : 0.f;
 
       // ---- pass 2: P = exp2(s * scale - m), packed over S's first 64 columns ----
-      if (split_p) {
-        if (permuted)
-          tile_exp_store<T, true, true, Mma16816<T>::kSplitP>(tS, p.scale_log2, m_ref, rel_limit, l_run);
-        else
-          tile_exp_store<T, false, true, Mma16816<T>::kSplitP>(tS, p.scale_log2, m_ref, rel_limit, l_run);
-      } else if (permuted) {
-        if (need_mask)
-          tile_exp_store<T, true, true, false>(tS, p.scale_log2, m_ref, rel_limit, l_run);
-        else
-          tile_exp_store<T, true, false, false>(tS, p.scale_log2, m_ref, rel_limit, l_run);
-      } else {
-        if (need_mask)
-          tile_exp_store<T, false, true, false>(tS, p.scale_log2, m_ref, rel_limit, l_run);
-        else
-          tile_exp_store<T, false, false, false>(tS, p.scale_log2, m_ref, rel_limit, l_run);
-      }
+      if (split_p)
+        tile_exp_store<T, true, Mma16816<T>::kSplitP>(tS, p.scale_log2, m_ref, rel_limit, l_run);
+      else if (need_mask)
+        tile_exp_store<T, true, false>(tS, p.scale_log2, m_ref, rel_limit, l_run);
+      else
+        tile_exp_store<T, false, false>(tS, p.scale_log2, m_ref, rel_limit, l_run);
       tmem_wait_st();
-      }
 
       // The last history tile may hold slots past the history length, and pages that were never
       // loaded: zero those V tokens in shared memory, because 0 * NaN would poison the accumulator.
@@ -983,14 +840,14 @@ inline bool encode_map(CUtensorMap* map, int dtype, int rank, const void* base, 
 // The five tensor maps of a call.  Encoding them costs several microseconds of host time, and a serving loop calls with
 // the same buffers and shapes step after step, so each host thread remembers the maps of its last few distinct calls.
 struct TcMaps {
-  CUtensorMap q, k, v, vpool, out;
+  CUtensorMap q, k, v, vpool, kpool, out;
 };
 struct TcMapKey {
-  const void *q, *k, *v, *vpool, *out;
+  const void *q, *k, *v, *vpool, *kpool, *out;
   long long rows, seqs, pages;
   int hq, hkv, d, tpp, dtype;
   bool operator==(const TcMapKey& o) const {
-    return q == o.q && k == o.k && v == o.v && vpool == o.vpool && out == o.out && rows == o.rows && seqs == o.seqs &&
+    return q == o.q && k == o.k && v == o.v && vpool == o.vpool && kpool == o.kpool && out == o.out && rows == o.rows && seqs == o.seqs &&
            pages == o.pages && hq == o.hq && hkv == o.hkv && d == o.d && tpp == o.tpp && dtype == o.dtype;
   }
 };
@@ -1008,7 +865,8 @@ const TcMaps* tensor_maps_for(const PrefillArgs& a) {
   // ragged batches: one flat row axis of total_tokens rows (the kernel adds each sequence's first row)
   const cuuint64_t S = a.cu_seqlens ? 1 : a.num_seqs, N = a.cu_seqlens ? (cuuint64_t)a.total_tokens : a.tokens_per_seq;
   const cuuint64_t Hq = a.num_q_heads, Hkv = a.num_kv_heads;
-  const TcMapKey key{a.q_prompt, a.k_prompt, a.v_prompt, a.num_pages > 0 ? a.v_pool : nullptr, a.out, (long long)N, (long long)S,
+  const TcMapKey key{a.q_prompt, a.k_prompt, a.v_prompt, a.num_pages > 0 ? a.v_pool : nullptr, a.num_pages > 0 ? a.k_pool : nullptr,
+                     a.out, (long long)N, (long long)S,
                      a.num_pages, a.num_q_heads, a.num_kv_heads, D, TPP, a.dtype};
   for (int i = 0; i < kSlots; ++i)
     if (cache[i].used && cache[i].key == key) return &cache[i].maps;
@@ -1037,8 +895,14 @@ const TcMaps* tensor_maps_for(const PrefillArgs& a) {
     const cuuint32_t box[3] = {(cuuint32_t)TPP, (cuuint32_t)D, 1};
     if (!encode_map(&m.vpool, a.dtype, 3, a.v_pool, dims, strides, box, TPP == 16 ? CU_TENSOR_MAP_SWIZZLE_32B : CU_TENSOR_MAP_SWIZZLE_64B))
       return nullptr;
+    // the K pool as rows of one (page, kv head, chunk) each: TPP tokens x 8 elements = TPP * 16 contiguous bytes
+    const cuuint64_t kdims[2] = {(cuuint64_t)TPP * 8, (cuuint64_t)a.num_pages * Hkv * (D / 8)};
+    const cuuint64_t kstrides[1] = {(cuuint64_t)TPP * 16};
+    const cuuint32_t kbox[2] = {(cuuint32_t)TPP * 8, 1};  // gather4 takes four such rows per request
+    if (!encode_map(&m.kpool, a.dtype, 2, a.k_pool, kdims, kstrides, kbox, CU_TENSOR_MAP_SWIZZLE_NONE)) return nullptr;
   } else {
     m.vpool = m.v;  // never dereferenced: without pages every history length is treated as 0
+    m.kpool = m.k;
   }
   slot.key = key;
   slot.used = true;
@@ -1055,7 +919,7 @@ int launch_tc(const TcParams& p, const TcMaps& m, cudaStream_t stream) {
   if (rc != 0) return rc;
   const int num_qt = (p.n_new + kTile - 1) / kTile;
   dim3 grid(PAIR_TILES ? (num_qt + 1) / 2 : num_qt, PAIR_TILES ? p.num_q_heads : p.num_q_heads / NQ, p.num_seqs);
-  kern<<<grid, 64 + 128 * NQ, C::kTotal, stream>>>(p, m.q, m.k, m.v, m.vpool, m.out);
+  kern<<<grid, 64 + 128 * NQ, C::kTotal, stream>>>(p, m.q, m.k, m.v, m.vpool, m.kpool, m.out);
   return (int)cudaGetLastError();
 }
 
@@ -1080,8 +944,8 @@ int launch_tc_shape(const PrefillArgs& a, cudaStream_t stream) {
     set_error("paged_attention_prefill: num_seqs and num_q_heads are limited to 65535");
     return -1;
   }
-  if ((long long)a.num_pages * a.num_kv_heads > 0x7fffffffLL) {
-    set_error("paged_attention_prefill: pool too large for the tcgen05 kernel (pages * kv_heads must fit 31 bits)");
+  if ((long long)a.num_pages * a.num_kv_heads * (D / 8) > 0x7fffffffLL) {
+    set_error("paged_attention_prefill: pool too large for the tcgen05 kernel (pages * kv_heads * head_dim / 8 must fit 31 bits)");
     return -2;
   }
   TcParams p;
