@@ -59,6 +59,10 @@ WORKLOADS = {
     "decode_70b_ctx_fused": dict(kind="decode", S=8, lo=131072, hi=131072, hq=64, hkv=8, d=128, tpp=16, partition_pages=256, ctx="fused",
                                  desc="Llama-3-70B long decode, context sharded: batch 8, context 131072 cut into N contiguous slices (one per GPU), "
                                       "64q/8kv heads, D=128, bf16, TPP=16, 256-page partitions, per-GPU (m,l,acc) exchanged by peer stores inside the combine kernel"),
+    "decode_70b_ctx_fused_auto": dict(kind="decode", S=8, lo=131072, hi=131072, hq=64, hkv=8, d=128, tpp=16, partition_pages=-1, ctx="fused",
+                                      desc="Llama-3-70B long decode, context sharded: batch 8, context 131072 cut into N contiguous slices (one per GPU), "
+                                           "64q/8kv heads, D=128, bf16, TPP=16, partition size chosen by the launcher, per-GPU (m,l,acc) exchanged by peer stores "
+                                           "inside the combine kernel"),
     "prefill_8b": dict(kind="prefill", S=8, n=2048, hlo=0, hhi=4096, hq=32, hkv=8, d=128, tpp=16,
                        desc="Llama-3-8B chunked causal prefill: 8 x 2048 new tokens, history U[0,4096], 32q/8kv heads, D=128, bf16, TPP=16"),
     "prefill_small": dict(kind="prefill", S=2, n=1024, hlo=0, hhi=2048, hq=32, hkv=8, d=128, tpp=16,
@@ -504,7 +508,7 @@ def prepare(name, env, pal, peaks, args, force_single=False):
         elif world > 1 and not ctx:
             w.extra_cfg["parallelism"] = f"sequence sharded x{world} (each GPU its own batch of {cfg['S']}), no collective"
         data = build_decode(cfg, device, seed=rank if (hkv_local is None and not ctx) else 0, hkv_local=hkv_local)
-        pp = cfg["partition_pages"]
+        pp = cfg["partition_pages"] if cfg["partition_pages"] > 0 or not ctx else None  # ctx forms: None = the library's choice
         if ctx and env.dist is not None and world > 1:
             env.dist.broadcast(data["q"], src=0)  # every rank must hold the same queries
         append = cfg.get("append")
@@ -731,7 +735,7 @@ def measure(w, env, peaks, steps, warmup, blocks, e2e=True):
 PROFILED_TRAFFIC = {"decode_8b": 1.3866e9, "decode_8b_append": 1.3889e9}
 
 EXTRA_SINGLE = ["prefill_8b", "decode_70b", "decode_70b_auto", "fill", "fill_append"]
-EXTRA_MULTI = ["decode_70b", "decode_70b_auto", "decode_70b_ctx", "decode_70b_ctx_fused", "prefill_8b"]
+EXTRA_MULTI = ["decode_70b", "decode_70b_auto", "decode_70b_ctx", "decode_70b_ctx_fused", "decode_70b_ctx_fused_auto", "prefill_8b"]
 
 
 def main():

@@ -125,6 +125,16 @@ def _decode_ws_bytes(S, hq, hkv, d, tpp, mp, pp) -> int:
     return lib.pal_decode_workspace_bytes(S, hq, hkv, d, tpp, mp, pp)
 
 
+def resolve_partition_pages(partition_pages, S, hq, hkv, d, tpp, max_pages) -> int:
+    """Partition size of a split-KV pass that always splits (the partials forms): a positive request is taken as it is,
+    ``None`` / ``PAL_DECODE_AUTO`` asks the library, and where the library would run a single pass the whole page table
+    is one partition."""
+    if partition_pages is not None and int(partition_pages) > 0:
+        return int(partition_pages)
+    pp = lib.pal_decode_auto_partition_pages(S, hq, hkv, d, tpp, max_pages) if (S > 0 and max_pages > 0) else 0
+    return pp if pp > 0 else max(int(max_pages), 1)
+
+
 def check_status(stream=None, device=None) -> None:
     """Raise ``RuntimeError`` if a kernel of the last call on this (device, stream) gave up a bounded wait.
 
@@ -250,30 +260,38 @@ def fill_kv_pages(
 # paged_attention_decode (src/proxy_attention_lab/ops.py:42-84, src/pal_core/src/ops.cpp:36-108)
 # ---------------------------------------------------------------------------------------------
 def _decode_shapes(queries, k_cache_pool, v_cache_pool, page_table, sequence_lengths):
-    for name, t in (("queries", queries), ("k_cache_pool", k_cache_pool), ("v_cache_pool", v_cache_pool),
-                    ("page_table", page_table), ("sequence_lengths", sequence_lengths)):
-        _need_cuda(name, t)
-    if v_cache_pool.dim() != 4 or k_cache_pool.dim() != 5:
+    # (this runs on every call: each tensor attribute is read once)
+    try:
+        on_gpu = queries.is_cuda and k_cache_pool.is_cuda and v_cache_pool.is_cuda and page_table.is_cuda and sequence_lengths.is_cuda
+    except AttributeError:
+        on_gpu = False
+    if not on_gpu:
+        for name, t in (("queries", queries), ("k_cache_pool", k_cache_pool), ("v_cache_pool", v_cache_pool),
+                        ("page_table", page_table), ("sequence_lengths", sequence_lengths)):
+            _need_cuda(name, t)
+    vs, ks, qs, ps = v_cache_pool.shape, k_cache_pool.shape, queries.shape, page_table.shape
+    if len(vs) != 4 or len(ks) != 5:
         raise ValueError("k_cache_pool must be 5-D and v_cache_pool 4-D")
-    num_pages, hkv, d, tpp = v_cache_pool.shape  # ops.cpp:50-60
-    if tuple(k_cache_pool.shape) != (num_pages, hkv, d // 8, tpp, 8):
+    num_pages, hkv, d, tpp = vs  # ops.cpp:50-60
+    if ks != (num_pages, hkv, d // 8, tpp, 8):
         raise ValueError("k_cache_pool shape does not match v_cache_pool")
     if not (k_cache_pool.is_contiguous() and v_cache_pool.is_contiguous()):
         raise ValueError("the page pools must be contiguous")
     if not (queries.dtype == k_cache_pool.dtype == v_cache_pool.dtype):
         raise ValueError("queries and both pools must share one dtype")
-    if page_table.dim() != 2:
+    if len(ps) != 2:
         raise ValueError("page_table must be 2-D [num_sequences, max_logical_pages]")
-    S = page_table.shape[0]
+    S = ps[0]
     # ops.cpp:62-66: the head count comes from a 3-D query only; the kernel then reads row s of the flat buffer as
     # Hq * D elements (paged_attention_decode.h.metal:106-108), whatever the number of dimensions.
-    hq = queries.shape[1] if queries.dim() == 3 else 1
-    if queries.dim() in (2, 3):
-        if queries.shape[-1] != d:
-            raise ValueError(f"queries head_dim {queries.shape[-1]} does not match the cache head_dim {d}")
-        if queries.shape[0] < S:
+    qdim = len(qs)
+    hq = qs[1] if qdim == 3 else 1
+    if qdim == 2 or qdim == 3:
+        if qs[-1] != d:
+            raise ValueError(f"queries head_dim {qs[-1]} does not match the cache head_dim {d}")
+        if qs[0] < S:
             raise ValueError("queries has fewer rows than page_table has sequences")
-    elif queries.dim() == 1:
+    elif qdim == 1:
         # a flat buffer of S rows of head_dim elements, one query head
         if queries.numel() < S * d or queries.numel() % d != 0:
             raise ValueError(f"1-D queries must hold a whole number (>= {S}) of rows of head_dim = {d} elements, got {queries.numel()} elements")
@@ -307,11 +325,14 @@ def paged_attention_decode(queries, k_cache_pool, v_cache_pool, page_table, sequ
         q = _contig(queries)
         pt = _index32("page_table", page_table)
         lens = _index32("sequence_lengths", sequence_lengths)
-        ws = _workspace(_decode_ws_bytes(S, hq, hkv, d, tpp, pt.shape[1], pp), dev, sp)
-        rc = lib.pal_paged_attention_decode(q.data_ptr(), _ptr(k_cache_pool), _ptr(v_cache_pool), _ptr(pt), lens.data_ptr(),
-                                            out.data_ptr(), S, hq, hkv, d, tpp, num_pages, pt.shape[1],
+        mp = pt.shape[1]
+        ws = _workspace(_decode_ws_bytes(S, hq, hkv, d, tpp, mp, pp), dev, sp)
+        rc = lib.pal_paged_attention_decode(q.data_ptr(), k_cache_pool.data_ptr() if num_pages else 0,
+                                            v_cache_pool.data_ptr() if num_pages else 0, pt.data_ptr() if mp else 0, lens.data_ptr(),
+                                            out.data_ptr(), S, hq, hkv, d, tpp, num_pages, mp,
                                             0.0 if scale is None else float(scale), code, pp, ws.data_ptr(), ws.numel(), sp)
-        _lib.check(rc)
+        if rc:
+            _lib.check(rc)
     return out
 
 
@@ -349,7 +370,7 @@ def paged_attention_decode_append(new_keys, new_values, queries, k_cache_pool, v
 
 
 def paged_attention_decode_partials(queries, k_cache_pool, v_cache_pool, page_table, sequence_lengths, *,
-                                    partition_pages: int = 256, scale=None, stream=None, packed: bool = False, out=None):
+                                    partition_pages=256, scale=None, stream=None, packed: bool = False, out=None):
     """Split-KV pass without the final normalisation: returns fp32 ``(m [S,Hq], l [S,Hq], acc [S,Hq,D])``.
 
     For callers that merge partial results themselves, e.g. GPUs that each hold a slice of every
@@ -359,6 +380,7 @@ def paged_attention_decode_partials(queries, k_cache_pool, v_cache_pool, page_ta
     """
     S, hq, hkv, d, tpp, num_pages = _decode_shapes(queries, k_cache_pool, v_cache_pool, page_table, sequence_lengths)
     dev = queries.device
+    partition_pages = resolve_partition_pages(partition_pages, S, hq, hkv, d, tpp, page_table.shape[1])
     with _Scope(dev, stream) as sp:
         if packed:
             if out is None:

@@ -128,11 +128,12 @@ class ContextExchange:
         torch.cuda.synchronize(self.device)
         dist.barrier(group)  # every rank's buffer is zero before anyone's first step
 
-    def decode(self, queries, k_cache_pool, v_cache_pool, page_table, sequence_lengths, *, partition_pages: int = 256,
+    def decode(self, queries, k_cache_pool, v_cache_pool, page_table, sequence_lengths, *, partition_pages=256,
                scale=None, out_dtype=None, stream=None):
         """``paged_attention_decode`` over a context that is sliced across the ranks: ``page_table`` / ``sequence_lengths``
         describe this rank's slice (length 0 where the rank holds nothing of a sequence), ``queries`` are the same on every
-        rank.  Returns the full ``[S, Hq, D]`` result on every rank."""
+        rank.  ``partition_pages=None`` lets the library size the partitions of the local split-KV pass.  Returns the full
+        ``[S, Hq, D]`` result on every rank."""
         from . import ops
 
         _lib, lib = self._lib, self._lib.lib
@@ -142,6 +143,7 @@ class ContextExchange:
         if S == 0 or page_table.shape[1] == 0:
             raise ValueError("every rank takes part in every step: the batch and the page table must not be empty")
         code, odt = ops._out_code(queries.dtype, out_dtype)
+        partition_pages = ops.resolve_partition_pages(partition_pages, S, hq, hkv, d, tpp, page_table.shape[1])
         with ops._Scope(self.device, stream) as sp:
             out = torch.empty((S, hq, d), dtype=odt, device=self.device)
             q = ops._contig(queries)

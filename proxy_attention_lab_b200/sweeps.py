@@ -7,6 +7,9 @@ history (``:292,382-388``), batch decode latency and throughput against the numb
 (``benchmarks/paged_attention/cpp/batch_latency_vs_num_sequences.cpp:258-268``).  The output nests
 ``benchmark -> sub-category -> group -> {parameter: value}`` as ``benchmarks/benchmarks.md:198-236`` describes;
 throughput is ``num_sequences / latency`` (``benchmarks/analyzer/plotters/batch_decode_latency.py:151``).
+``fill_kv_pages`` is swept as the reference's pytest-benchmark file does
+(``benchmarks/fill_kv_pages/python/test_fill_kv_pages_python.py:13,73,136-137``): new tokens of one sequence, one token each
+of many sequences (sequences sharing pages), and head_dim x kv heads at 32 tokens; 8 kv heads, D = 128, TPP = 16 otherwise.
 The group name is ``cuda_pal_b200`` where the reference writes ``cpp_pal``.
 
     python -m proxy_attention_lab_b200.sweeps --out results.json [--quick]
@@ -74,6 +77,28 @@ def prefill_point(pal, device, seq_len: int, timing) -> float:
     return _time_ms(lambda: pal.paged_attention_prefill(q, k, v, k_pool, v_pool, table, hist), *timing)
 
 
+def fill_point(pal, device, timing, *, tokens: int = 0, sequences: int = 0, hkv: int = 8, d: int = 128, dtype=torch.bfloat16) -> float:
+    """Latency of one fill_kv_pages call: `tokens` consecutive tokens of one sequence, or one token each of `sequences`
+    sequences whose pages are shared two to a page (the reference's two set-ups)."""
+    gen = torch.Generator(device=device).manual_seed(tokens * 7 + sequences)
+    n = tokens or sequences
+    if tokens:
+        pages = max(4, tokens // TPP + 2)
+        table = torch.arange((tokens + TPP - 1) // TPP, dtype=torch.int32, device=device).reshape(1, -1)
+        pos = torch.arange(tokens, dtype=torch.int32, device=device)
+        seq = torch.zeros(tokens, dtype=torch.int32, device=device)
+    else:
+        pages = max(4, sequences // 2)
+        table = (torch.arange(sequences, dtype=torch.int32, device=device) % pages).reshape(sequences, 1)
+        pos = torch.arange(sequences, dtype=torch.int32, device=device) % TPP
+        seq = torch.arange(sequences, dtype=torch.int32, device=device)
+    keys = torch.randn((n, hkv, d), device=device, dtype=dtype, generator=gen)
+    vals = torch.randn((n, hkv, d), device=device, dtype=dtype, generator=gen)
+    k_pool = torch.zeros((pages, hkv, d // 8, TPP, 8), device=device, dtype=dtype)
+    v_pool = torch.zeros((pages, hkv, d, TPP), device=device, dtype=dtype)
+    return _time_ms(lambda: pal.fill_kv_pages(keys, vals, k_pool, v_pool, table, pos, seq), *timing)
+
+
 def run(pal, device, quick: bool, timing) -> dict:
     decode_hist = [64, 256, 1024, 4096] if quick else [64 << i for i in range(14)]           # 64 .. 524288
     prefill_len = [64, 256, 1024] if quick else [64, 128, 256, 512, 1024, 2048, 4096]
@@ -93,6 +118,16 @@ def run(pal, device, quick: bool, timing) -> dict:
             thr[str(s)] = s / (ms * 1e-3)
         out["batch_decode_latency"]["latency_vs_num_sequences"][f"H={h}"] = lat
         out["batch_decode_latency"]["throughput_vs_num_sequences"][f"H={h}"] = thr
+    fill = {"latency_vs_num_new_tokens": {}, "latency_vs_num_sequences": {}, "latency_vs_dimensions": {GROUP: {}}}
+    for name, dtype in (("float16", torch.float16), ("bfloat16", torch.bfloat16)):
+        fill["latency_vs_num_new_tokens"][f"{GROUP}_{name}"] = {
+            str(t): fill_point(pal, device, timing, tokens=t, dtype=dtype) for t in ([1, 16, 128] if quick else [1, 4, 8, 16, 32, 64, 128])}
+        fill["latency_vs_num_sequences"][f"{GROUP}_{name}"] = {
+            str(n): fill_point(pal, device, timing, sequences=n, dtype=dtype) for n in ([1, 8, 64] if quick else [1, 2, 4, 8, 16, 32, 64])}
+    for d in ([128] if quick else [64, 128, 256]):
+        for hkv in ([8] if quick else [1, 4, 8, 16]):
+            fill["latency_vs_dimensions"][GROUP][f"D={d},Hkv={hkv}"] = fill_point(pal, device, timing, tokens=32, hkv=hkv, d=d, dtype=torch.float16)
+    out["fill_kv_pages"] = fill
     return out
 
 

@@ -20,7 +20,11 @@ def test_quick_sweep_schema(tmp_path):
     out = tmp_path / "results.json"
     assert sweeps.main(["--out", str(out), "--quick", "--warmup", "1", "--iters", "2", "--reps", "2"]) == 0
     r = json.loads(out.read_text())
-    assert set(r) == {"latency_vs_seq_len", "batch_decode_latency"}
+    assert set(r) == {"latency_vs_seq_len", "batch_decode_latency", "fill_kv_pages"}
+    fill = r["fill_kv_pages"]
+    assert set(fill) == {"latency_vs_num_new_tokens", "latency_vs_num_sequences", "latency_vs_dimensions"}
+    for series in list(fill["latency_vs_num_new_tokens"].values()) + list(fill["latency_vs_num_sequences"].values()) + list(fill["latency_vs_dimensions"].values()):
+        assert series and all(v > 0 for v in series.values())
     for kind in ("prefill", "decode"):
         series = r["latency_vs_seq_len"][kind][sweeps.GROUP]
         assert series and all(float(k) > 0 and v > 0 for k, v in series.items())
