@@ -67,6 +67,8 @@ WORKLOADS = {
                        desc="Llama-3-8B chunked causal prefill: 8 x 2048 new tokens, history U[0,4096], 32q/8kv heads, D=128, bf16, TPP=16"),
     "prefill_small": dict(kind="prefill", S=2, n=1024, hlo=0, hhi=2048, hq=32, hkv=8, d=128, tpp=16,
                           desc="reduced chunked prefill for profiler captures: 2 x 1024 new tokens, history U[0,2048], 32q/8kv heads, D=128, bf16, TPP=16"),
+    "prefill_wave": dict(kind="prefill", S=4, n=2048, hlo=2048, hhi=2048, hq=32, hkv=8, d=128, tpp=16,
+                         desc="one full wave of prefill CTAs for profiler captures: 4 x 2048 new tokens, history 2048, 32q/8kv heads, D=128, bf16, TPP=16"),
     "prefill_ragged": dict(kind="prefill", S=8, n=2048, nlo=128, hlo=0, hhi=4096, hq=32, hkv=8, d=128, tpp=16,
                            desc="ragged chunked causal prefill (paged_attention_prefill_ragged): 8 sequences with U[128,2048] new tokens each, "
                                 "history U[0,4096], 32q/8kv heads, D=128, bf16, TPP=16"),
@@ -709,7 +711,7 @@ def measure(w, env, peaks, steps, warmup, blocks, e2e=True):
         # tensor-bound: short blocks separated by idle gaps run at burst clocks and are compared with the burst peak (itself
         # the best of ten short GEMMs); one block of about a second, under the power cap, is compared with the sustained peak
         peak, rec["peak_kind"] = (peaks["tensor"], "burst: 0.1 s idle before every block") if burst else (peaks["tensor_sustained"], "sustained")
-        if burst:
+        if burst and not getattr(w, "no_sustained", False):
             long_steps = max(steps, int(1.0 / max(sec_med / steps, 1e-6)))
             sec_long = timed_blocks(env, step, long_steps, 0, 1)[0]
             sustained = units * long_steps / sec_long / w.scale
@@ -750,6 +752,7 @@ def main():
     ap.add_argument("--prefill-impl", default="auto")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-cuda-graph", action="store_true", help="context-sharded workloads: enqueue every step from the host")
+    ap.add_argument("--no-sustained", action="store_true", help="tensor-bound workloads: skip the one-second block (profiler captures)")
     args = ap.parse_args()
     cfg = WORKLOADS[args.workload]
     env = Env()
@@ -767,6 +770,7 @@ def main():
     peaks = measured_peaks()
 
     head = prepare(args.workload, env, pal, peaks, args)
+    head.no_sustained = args.no_sustained
     rec = measure(head, env, peaks, args.steps, args.warmup, args.blocks)
     line = {
         "metric": rec["metric"], "value": rec["value"], "unit": rec["unit"], "n_gpus": env.world, "steps": args.steps, "warmup": args.warmup,
@@ -815,6 +819,7 @@ def main():
                 records[name] = {"unavailable": f"{wcfg['hkv']} kv heads do not divide over {env.world} GPUs"}
                 continue
             w = prepare(name, env, pal, peaks, args)
+            w.no_sustained = args.no_sustained
             r = measure(w, env, peaks, steps_n, max(3, min(args.warmup, 5)), x_blocks)
             if env.world > 1 and w.scaling == "strong":
                 # the same problem on ONE GPU, run by every rank at the same time: the N = 1 figure of this very run
