@@ -732,8 +732,8 @@ def measure(w, env, peaks, steps, warmup, blocks, e2e=True):
     return rec
 
 
-# DRAM bytes per launch from `ncu --set full` captures of the same workloads (summaries under profiles/), not measured
-# in this run; fill_append is 0.904 x its algorithmic bytes (captured on the reduced case; the traffic grows with the tokens).
+# DRAM bytes per launch from `ncu --set full` captures of the same workloads, not measured in this run; fill_append is
+# 0.904 x its algorithmic bytes (captured on the reduced case; the traffic grows with the tokens).
 PROFILED_TRAFFIC = {"decode_8b": 1.3866e9, "decode_8b_append": 1.3889e9}
 
 EXTRA_SINGLE = ["prefill_8b", "decode_70b", "decode_70b_auto", "fill", "fill_append"]
@@ -776,12 +776,13 @@ def main():
         "metric": rec["metric"], "value": rec["value"], "unit": rec["unit"], "n_gpus": env.world, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": rec["ms_per_step"], "higher_is_better": True, "scaling": rec["scaling"], "vs_baseline": None,
         "dtype": "bf16 (f32 accumulate)", "data": "synthetic",
-        "config": {"workload": cfg["desc"], **head.extra_cfg},
+        "config": {"workload": cfg["desc"]},
         "blocks": args.blocks, "value_best_block": rec["value_best_block"], "timing": "median of the timed blocks; each block is exactly `steps` steps",
         "l2": rec["l2"], "tokens_per_s": rec["tokens_per_s"], "e2e": rec.get("e2e"),
         "gpu_launches": head.launches_per_step * args.steps * args.blocks,
         "clocks": rec["clocks"], "roofline": dict(rec["roofline"]),
     }
+    line.update(head.extra_cfg)  # how the workload is spread over the GPUs, beside `config` (which both arms share)
     if "cuda_graph" in rec:
         line["cuda_graph"] = rec["cuda_graph"]
     traffic = PROFILED_TRAFFIC.get(args.workload) if env.world == 1 else None

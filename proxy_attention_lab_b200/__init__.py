@@ -4,7 +4,7 @@ Exports the names of ``src/proxy_attention_lab/__init__.py:17-37`` plus the spli
 blocks used for multi-GPU long-context decode.
 """
 
-from . import pal_core  # noqa: F401
+from . import pal_core, sharding  # noqa: F401
 from .ops import (  # noqa: F401
     fill_kv_pages,
     get_k_cache_shape,
