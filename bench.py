@@ -10,7 +10,7 @@ decode (kv-head sharded; context sharded with the NCCL all-gather + combine; con
 peer-store exchange).  ``--workload NAME`` makes another workload the headline; ``--workloads none`` leaves the
 extra records out (profiler captures use that).
 
-Every figure is the median over ``--blocks`` timed blocks of K steps each (barrier + synchronize around every
+Every figure is the median over ``--blocks`` (default 20) timed blocks of K steps each (barrier + synchronize around every
 block, CUDA events on the launching stream, max over ranks); the fastest block is reported beside it.
 
 ``--impl reference`` times the reference side of the comparison instead.  Proxy Attention Lab has no
@@ -745,7 +745,7 @@ def main():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=500)
     ap.add_argument("--warmup", type=int, default=10)
-    ap.add_argument("--blocks", type=int, default=10, help="timed blocks of --steps steps each; the median block is reported")
+    ap.add_argument("--blocks", type=int, default=20, help="timed blocks of --steps steps each; the median block is reported")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="decode_8b", choices=sorted(WORKLOADS), help="the headline workload")
     ap.add_argument("--workloads", default="all", help="extra records in the same line: all | none | comma-separated names")

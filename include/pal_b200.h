@@ -123,9 +123,10 @@ size_t pal_decode_workspace_bytes(int num_seqs, int num_q_heads, int num_kv_head
                                   int tokens_per_page, int max_pages_per_seq, int partition_pages);
 
 /* The partition size PAL_DECODE_AUTO resolves to for this problem: 0 (single pass) when the batch alone gives
- * every SM a couple of (sequence, kv head) work items, otherwise the number of pages per partition that makes
- * the work items fill whole waves of the resident CTAs (two per SM) at the least modelled time - streaming time
- * of a partition plus a fixed cost per work item, times the number of waves - and never below 16 pages.  The
+ * every resident CTA (two per SM) a (sequence, kv head) work item, otherwise the number of pages per partition
+ * with the least modelled step time - the larger of the HBM time of all pages and the busiest CTA's own streaming
+ * time, plus a fixed cost per work item and per partition merged: as few partitions as still keep most CTAs
+ * busy in one wave, never below 16 pages.  The
  * reference switches to two passes by page-table width alone, with fixed 512-token chunks
  * (src/pal_core/src/paged_attention_decode_primitive.cpp:100-102). */
 int pal_decode_auto_partition_pages(int num_seqs, int num_q_heads, int num_kv_heads, int head_dim,

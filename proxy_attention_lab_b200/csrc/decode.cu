@@ -579,17 +579,30 @@ __global__ void __launch_bounds__(128) lse_combine_kernel(const PartialsView in,
   float den_all = 0.f;
   for (int w = 0; w < (int)(blockDim.x >> 5); ++w) den_all += s_red[w];
   const float* ar = in.acc + row * in.row_stride_acc;
+  auto weight = [&](int j) {
+    if (j < 1024) return s_w[j];
+    const float mj = mr[j * in.part_stride_ml];
+    return (mj > -INFINITY) ? __expf(mj - M) : 0.f;
+  };
   for (int d = threadIdx.x; d < head_dim; d += blockDim.x) {
+    // Eight partitions' values are requested before the first is used: the loop is bound by the latency of its loads,
+    // not by their number.  The sum is still taken in partition order.
     float num = 0.f;
-    for (int j = 0; j < num_parts; ++j) {
-      float w;
-      if (j < 1024) {
-        w = s_w[j];
-      } else {
-        const float mj = mr[j * in.part_stride_ml];
-        w = (mj > -INFINITY) ? __expf(mj - M) : 0.f;
+    int j = 0;
+    for (; j + 8 <= num_parts; j += 8) {
+      float a[8], w[8];
+#pragma unroll
+      for (int k = 0; k < 8; ++k) {
+        w[k] = weight(j + k);
+        a[k] = ar[(long long)(j + k) * in.part_stride_acc + d];
       }
-      if (w != 0.f) num += w * ar[j * in.part_stride_acc + d];
+#pragma unroll
+      for (int k = 0; k < 8; ++k)
+        if (w[k] != 0.f) num = fmaf(w[k], a[k], num);
+    }
+    for (; j < num_parts; ++j) {
+      const float w = weight(j);
+      if (w != 0.f) num = fmaf(w, ar[(long long)j * in.part_stride_acc + d], num);
     }
     if (out) {
       const float v = den_all > 0.f ? num / den_all : 0.f;
@@ -672,12 +685,13 @@ int decode_num_partitions(int max_pages_per_seq, int partition_pages) {
   return n < 1 ? 1 : n;
 }
 
-// Two-pass when the batch alone cannot give every SM a couple of work items.  The number of partitions per sequence is
-// then the one with the least modelled step time: the work items run in waves over the resident CTAs (two per SM), a wave
-// lasts as long as one item - its pages at one CTA's share of the memory bandwidth plus a fixed cost per item (scheduling,
-// query load, the merge of the four warps, the partial write; about 3 us measured) - and partial waves cost a whole one.
-// Measured on B200 with 8 sequences x 131072 tokens: one kv head per GPU runs 256-page partitions (256 items, one per CTA
-// with 40 CTAs idle) in 101 us, and 128-page partitions (512 items, 1.7 waves) in 126 us.
+// Two-pass when the batch alone cannot give every resident CTA (two per SM) a work item.  The number of partitions per
+// sequence is then the one with the least modelled step time.  Measured on B200 (8 sequences x 131072 tokens, whole and
+// under 8-way kv-head / context sharding): a step costs the larger of the HBM time of all its pages and the time the
+// busiest CTA needs for its own pages (with ~200 CTAs active one CTA sustains about 28 GB/s: 64 KB in flight per ~2 us),
+// plus about 1.3 us per work item a CTA handles and 75 ns per partition in the combine kernel.  So partitions should be
+// as few as still give the memory system enough CTAs: e.g. one kv head per GPU runs 256-page partitions (256 items) in
+// 92.7 us, 512-page ones (128 items, too few CTAs) in ~118 us and 64-page ones (1024 items) in 109 us.
 int decode_auto_partition_pages(int num_seqs, int num_q_heads, int num_kv_heads, int head_dim, int tokens_per_page,
                                 int max_pages_per_seq) {
   const int group = num_q_heads / num_kv_heads;
@@ -685,22 +699,24 @@ int decode_auto_partition_pages(int num_seqs, int num_q_heads, int num_kv_heads,
   const long long base = (long long)num_seqs * num_kv_heads * ((group + hpi - 1) / hpi);
   const long long slots = 2LL * cached_sm_count();
   if (base >= slots || max_pages_per_seq <= 32) return 0;
-  // nanoseconds to stream one page's K and V blocks at 1/slots of ~6.6 TB/s
-  const double page_ns = (double)head_dim * tokens_per_page * 4.0 * (double)slots / 6600.0;
-  const double item_ns = 3000.0;
+  const double page_bytes = (double)head_dim * tokens_per_page * 4.0;  // K and V block of one page
+  const double hbm_ns = (double)base * max_pages_per_seq * page_bytes / 6600.0;  // 6.6 TB/s = 6600 bytes per ns
+  const double page_ns = page_bytes / 28.0;                                       // one CTA among ~200 active: 28 GB/s
   int best_parts = 1;
   double best = 1e30;
   const int max_parts = max_pages_per_seq / 16;
   for (int parts = 1; parts <= max_parts && parts <= 4096; ++parts) {
     const int pp = (max_pages_per_seq + parts - 1) / parts;
-    const long long items = base * ((max_pages_per_seq + pp - 1) / pp);
+    const int real_parts = (max_pages_per_seq + pp - 1) / pp;
+    const long long items = base * real_parts;
     const long long waves = (items + slots - 1) / slots;
-    const double t = (double)waves * (pp * page_ns + item_ns);
-    if (t < best * 0.999) {  // ties go to fewer, larger partitions
+    const double stream = fmax(hbm_ns, (double)waves * pp * page_ns);
+    const double t = stream + waves * 1300.0 + real_parts * 75.0;
+    if (t < best * 0.995) {  // ties go to fewer, larger partitions
       best = t;
       best_parts = parts;
     }
-    if (items > 64 * slots) break;
+    if (items > 16 * slots) break;
   }
   const int pp = (max_pages_per_seq + best_parts - 1) / best_parts;
   return pp >= max_pages_per_seq ? 0 : pp;

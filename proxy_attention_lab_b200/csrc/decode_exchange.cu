@@ -100,17 +100,30 @@ __global__ void __launch_bounds__(kExchangeThreads, 8) ctx_exchange_combine_kern
     __syncthreads();
     const float den_all = (s_red[4] + s_red[5]) + (s_red[6] + s_red[7]);
     const float* ar = p.in.acc + row * p.in.row_stride_acc;
+    auto weight = [&](int j) {
+      if (j < 1024) return s_w[j];
+      const float mj = mr[j * p.in.part_stride_ml];
+      return (mj > -INFINITY) ? __expf(mj - M) : 0.f;
+    };
     for (int d = tid; d < D; d += kExchangeThreads) {
+      // eight partitions' values in flight at a time (the loop is latency-bound); summed in partition order, exactly as
+      // lse_combine_kernel does, so that the two forms of the merge agree bit for bit
       float num = 0.f;
-      for (int j = 0; j < p.num_parts; ++j) {
-        float w;
-        if (j < 1024) {
-          w = s_w[j];
-        } else {
-          const float mj = mr[j * p.in.part_stride_ml];
-          w = (mj > -INFINITY) ? __expf(mj - M) : 0.f;
+      int j = 0;
+      for (; j + 8 <= p.num_parts; j += 8) {
+        float a[8], w[8];
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+          w[k] = weight(j + k);
+          a[k] = ar[(long long)(j + k) * p.in.part_stride_acc + d];
         }
-        if (w != 0.f) num += w * ar[j * p.in.part_stride_acc + d];
+#pragma unroll
+        for (int k = 0; k < 8; ++k)
+          if (w[k] != 0.f) num = fmaf(w[k], a[k], num);
+      }
+      for (; j < p.num_parts; ++j) {
+        const float w = weight(j);
+        if (w != 0.f) num = fmaf(w, ar[(long long)j * p.in.part_stride_acc + d], num);
       }
       for (int r = 0; r < p.world; ++r) {
         float* dst = reinterpret_cast<float*>(p.peer[r] + kStateBytes + kFlagBytes) +
@@ -176,10 +189,14 @@ __global__ void __launch_bounds__(kExchangeThreads, 8) ctx_exchange_combine_kern
       }
     }
     for (int d = tid; d < D; d += kExchangeThreads) {
+      float a[kMaxPeers];
+#pragma unroll
+      for (int r = 0; r < kMaxPeers; ++r)  // all ranks' values requested before the first is used
+        a[r] = r < p.world ? __ldcg(gather + ((long long)r * p.rows_capacity + row) * pitch + d) : 0.f;
       float num = 0.f;
 #pragma unroll
       for (int r = 0; r < kMaxPeers; ++r)
-        if (r < p.world && w[r] != 0.f) num += w[r] * __ldcg(gather + ((long long)r * p.rows_capacity + row) * pitch + d);
+        if (r < p.world && w[r] != 0.f) num = fmaf(w[r], a[r], num);
       const float v = den > 0.f ? num / den : 0.f;
       if (p.out_f32)
         static_cast<float*>(p.out)[row * D + d] = v;

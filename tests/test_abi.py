@@ -142,3 +142,22 @@ def test_out_f32_flag_and_new_entry_points_validate():
     assert lib.pal_check_status(None, None) == _lib.PAL_ERR_BAD_ARG
     rc = lib.pal_paged_attention_decode_partials_packed(None, None, None, None, None, None, 1, 2, 2, 64, 16, 1, 1, 0.0, 0, 0, None, 0, None)
     assert rc == _lib.PAL_ERR_BAD_ARG and "partition_pages" in _lib.last_error()
+
+
+def test_auto_partition_size_gives_the_memory_system_enough_ctas():
+    """PAL_DECODE_AUTO: single pass when the batch alone fills the GPU; otherwise as few partitions as still put a work
+    item on most of the resident CTAs (two per SM; 148 SMs assumed when no device is present) in a single wave."""
+    from proxy_attention_lab_b200 import _lib, ops
+
+    f = _lib.lib.pal_decode_auto_partition_pages
+    assert f(64, 32, 8, 128, 16, 512) == 0            # Llama-3-8B batch: 512 work items, single pass
+    assert f(4, 8, 2, 128, 16, 32) == 0               # short contexts are never split
+    for seqs, hq, hkv, mp in ((8, 8, 1, 8192), (8, 64, 8, 8192), (8, 64, 8, 1024), (8, 32, 4, 8192)):
+        pp = f(seqs, hq, hkv, 128, 16, mp)            # the 70B long-context shape, whole and sharded 8 ways
+        items = seqs * hkv * -(-mp // pp)
+        assert 16 <= pp < mp and 200 <= items <= 296, (seqs, hkv, mp, pp, items)
+    assert f(0, 8, 1, 128, 16, 8192) == 0 and f(8, 8, 1, 128, 16, 0) == 0
+    # the forms that always split fall back to one partition where the launcher would not split at all
+    assert ops.resolve_partition_pages(None, 64, 32, 8, 128, 16, 512) == 512
+    assert ops.resolve_partition_pages(37, 64, 32, 8, 128, 16, 512) == 37
+    assert ops.resolve_partition_pages(-1, 8, 8, 1, 128, 16, 8192) == f(8, 8, 1, 128, 16, 8192)
