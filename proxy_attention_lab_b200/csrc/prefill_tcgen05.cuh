@@ -334,6 +334,31 @@ struct Fmt<__nv_bfloat16> {
   static constexpr int kCode = 1;
 };
 
+// The grid's z index counts sequences in order of decreasing work (history plus new tokens), so that the CTAs launched
+// last - the ones that run while the SMs drain - belong to the sequence whose CTAs are shortest.  With the sequences in
+// the caller's order a long last sequence leaves a tail in which most SMs idle (simulated for the benchmark batch, whose
+// last sequence is its longest: 95 % -> 97 % of the SM-time used).  The order inside a sequence is unchanged: its query
+// tiles stay neighbours in launch order and share its history tiles in L2.  Every warp computes the mapping for itself
+// (batches of up to 32 sequences: one key per lane, ranked with shuffles); larger batches keep the caller's order.
+// (In two steps, so that the loads of the keys can be in flight while the CTA sets itself up.)
+__device__ __forceinline__ int sequence_rank_key(const TcParams& p, int lane) {
+  if (p.num_seqs > 32 || p.num_seqs < 2 || lane >= p.num_seqs) return -1;
+  int h = p.hist_lens[lane];
+  h = h < 0 ? 0 : h;
+  const int n = p.cu_seqlens ? p.cu_seqlens[lane + 1] - p.cu_seqlens[lane] : 0;
+  return min(h, 0x3fffffff) + min(max(n, 0), 0x3fffffff);
+}
+__device__ __forceinline__ int sequence_of_rank(const TcParams& p, int z, int lane, int key) {
+  if (p.num_seqs > 32 || p.num_seqs < 2) return z;
+  int rank = 0;
+  for (int j = 0; j < p.num_seqs; ++j) {
+    const int kj = __shfl_sync(0xffffffffu, key, j);
+    rank += (kj > key || (kj == key && j < lane)) ? 1 : 0;
+  }
+  const unsigned hit = __ballot_sync(0xffffffffu, lane < p.num_seqs && rank == z);
+  return hit ? __ffs(hit) - 1 : z;
+}
+
 // NQ accumulator tiles per CTA.  PAIR_TILES = false: tile q is query head h0 + q of one 128-token query tile (heads that
 // share a kv head).  PAIR_TILES = true (NQ = 2): both tiles belong to head h0, tile q holds query tile 2 * blockIdx.x' + q;
 // they share every K / V tile, and the earlier one sees its last key tile fully masked.
@@ -362,22 +387,53 @@ __global__ void __launch_bounds__(64 + 128 * NQ, 1)
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 15);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  // heaviest (latest) query tiles first
-  const int qt_cta = (int)gridDim.x - 1 - (int)blockIdx.x;
+  // Launch order (x fastest): all heads of a sequence's heaviest (latest) query tile, then its next query tile, ... so
+  // the CTAs of one sequence run together (its K / V tiles are shared in L2) and the last ones of the grid are light.
+  const int qt_cta = (int)gridDim.y - 1 - (int)blockIdx.y;
   const int qt = PAIR_TILES ? 2 * qt_cta : qt_cta;   // the CTA's first (or only) query tile
   const int t0 = qt * kTile;
-  const int h0 = PAIR_TILES ? blockIdx.y : blockIdx.y * NQ;
+  const int h0 = PAIR_TILES ? blockIdx.x : blockIdx.x * NQ;
   constexpr int kHeadStep = PAIR_TILES ? 0 : 1;         // head of accumulator tile q = h0 + q * kHeadStep
   constexpr int kRowStep = PAIR_TILES ? kTile : 0;      // its first query token = t0 + q * kRowStep
-  const int s = blockIdx.z;
+  // Barriers and tensor memory; for uniform batches this runs while the keys that order the sequences are being loaded.
+  auto set_up = [&] {
+    if (tid == 0) {
+      mbar_init(q_full, 1);
+      for (int i = 0; i < 2; ++i) {
+        mbar_init(&k_full[i], 1);
+        mbar_init(&k_empty[i], 1);
+        mbar_init(&v_full[i], 1);
+        mbar_init(&v_empty[i], 1);
+        mbar_init(&s_full[i], 1);
+        mbar_init(&p_full[i], 4);
+        mbar_init(&o_done[i], 1);
+      }
+      fence_mbar_init();
+    }
+    if (warp == 1) {
+      asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(512u)
+                   : "memory");
+      asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+  };
+  const bool ragged = p.cu_seqlens != nullptr;
+  const int rank_key = sequence_rank_key(p, lane);
+  if (!ragged) {
+    if (t0 >= p.n_new) return;
+    set_up();
+  }
+  const int s = sequence_of_rank(p, blockIdx.z, lane, rank_key);
   const int kvh = h0 / p.group;
   // Uniform batches index the prompt tensors as [sequence][token] (rows past N read as zero); ragged batches as one
   // flat row axis starting at the sequence's first row (rows past N belong to the next sequence and are masked).
-  const int N = p.cu_seqlens ? p.cu_seqlens[s + 1] - p.cu_seqlens[s] : p.n_new;
-  const int row0 = p.cu_seqlens ? p.cu_seqlens[s] : 0;
-  const int tma_seq = p.cu_seqlens ? 0 : s;
-  const size_t out_row0 = p.cu_seqlens ? (size_t)row0 : (size_t)s * N;
-  if (t0 >= N) return;  // ragged: the grid is sized for the longest sequence (nothing is allocated yet)
+  const int N = ragged ? p.cu_seqlens[s + 1] - p.cu_seqlens[s] : p.n_new;
+  const int row0 = ragged ? p.cu_seqlens[s] : 0;
+  const int tma_seq = ragged ? 0 : s;
+  const size_t out_row0 = ragged ? (size_t)row0 : (size_t)s * N;
+  if (ragged) {
+    if (t0 >= N) return;  // the grid is sized for the longest sequence (nothing is allocated yet)
+    set_up();
+  }
   int H = p.hist_lens[s];
   if (H < 0 || p.num_pages <= 0) H = 0;
   {
@@ -398,24 +454,6 @@ __global__ void __launch_bounds__(64 + 128 * NQ, 1)
   // including rows dominated by a single key, where the rounding of P shows undiluted: the residual is then always fed.
   const bool split_p = Mma16816<T>::kSplitP && (p.out_f32 != 0 || H + t0 < 256);
 
-  if (tid == 0) {
-    mbar_init(q_full, 1);
-    for (int i = 0; i < 2; ++i) {
-      mbar_init(&k_full[i], 1);
-      mbar_init(&k_empty[i], 1);
-      mbar_init(&v_full[i], 1);
-      mbar_init(&v_empty[i], 1);
-      mbar_init(&s_full[i], 1);
-      mbar_init(&p_full[i], 4);
-      mbar_init(&o_done[i], 1);
-    }
-    fence_mbar_init();
-  }
-  if (warp == 1) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(512u)
-                 : "memory");
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
-  }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
@@ -918,7 +956,11 @@ int launch_tc(const TcParams& p, const TcMaps& m, cudaStream_t stream) {
   const int rc = configured.run([&] { return (int)cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kTotal); });
   if (rc != 0) return rc;
   const int num_qt = (p.n_new + kTile - 1) / kTile;
-  dim3 grid(PAIR_TILES ? (num_qt + 1) / 2 : num_qt, PAIR_TILES ? p.num_q_heads : p.num_q_heads / NQ, p.num_seqs);
+  dim3 grid(PAIR_TILES ? p.num_q_heads : p.num_q_heads / NQ, PAIR_TILES ? (num_qt + 1) / 2 : num_qt, p.num_seqs);
+  if (grid.y > 65535) {
+    set_error("paged_attention_prefill: more than 65535 query tiles per sequence");
+    return -2;
+  }
   kern<<<grid, 64 + 128 * NQ, C::kTotal, stream>>>(p, m.q, m.k, m.v, m.vpool, m.kpool, m.out);
   return (int)cudaGetLastError();
 }
