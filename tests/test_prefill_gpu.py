@@ -148,3 +148,16 @@ def test_odd_head_groups_pair_query_tiles(pal, cuda, dtype, hist, n, hq, hkv):
     counts, a sequence of exactly one tile, with and without history)."""
     check(pal, cuda, make_prefill_case(7, hist, n, hq, hkv, 128, dtype=dtype), "tcgen05")
 
+
+
+@pytest.mark.parametrize("impl", ["tcgen05", "tcgen05_single"])
+@pytest.mark.parametrize("num_seqs", [2, 31, 32, 33, 40])
+def test_sequences_are_processed_in_order_of_work(pal, cuda, impl, num_seqs):
+    """The tcgen05 kernel hands its grid's z index to the sequences in order of decreasing history (batches of up to 32
+    sequences; larger ones keep the caller's order).  Every sequence must still be computed exactly once: histories
+    with ties, zeros and a maximum in the middle, on both sides of the 32-sequence limit."""
+    hist = [(37 * i) % 150 for i in range(num_seqs)]
+    hist[num_seqs // 2] = 300
+    hist[-1] = hist[0]
+    case = make_prefill_case(400 + num_seqs, hist, 64, 4, 2, 128, dtype=torch.bfloat16, poison_unused=True)
+    check(pal, cuda, case, impl)

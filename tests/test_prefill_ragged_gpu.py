@@ -92,6 +92,20 @@ def test_other_shapes_mma(pal, cuda, d, tpp):
     check(pal, cuda, make_ragged_case(13, hist, counts, 6, 3, d, tpp=tpp), "mma")
 
 
+@pytest.mark.parametrize("impl", ["tcgen05", "tcgen05_single"])
+@pytest.mark.parametrize("num_seqs", [5, 32, 35])
+def test_ragged_batches_ordered_by_work(pal, cuda, impl, num_seqs):
+    """The tcgen05 kernel takes the sequences of a batch in order of decreasing history + new tokens (up to 32 sequences);
+    counts and histories with ties, a count of 1 and the longest sequence in the middle."""
+    counts = [1 + (53 * i) % 140 for i in range(num_seqs)]
+    hist = [(29 * i) % 90 for i in range(num_seqs)]
+    counts[num_seqs // 2], hist[num_seqs // 2] = 200, 260
+    counts[-1], hist[-1] = counts[0], hist[0]
+    counts[1] = 1
+    c = make_ragged_case(600 + num_seqs, hist, counts, 4, 2, 128, poison_unused=True)
+    check(pal, cuda, c, impl)
+
+
 @pytest.mark.parametrize("impl", IMPLS)
 def test_equal_counts_match_the_uniform_call_bit_for_bit(pal, cuda, impl):
     counts = [192] * 3
