@@ -434,6 +434,14 @@ __global__ void __launch_bounds__(64 + 128 * NQ, 1)
     if (t0 >= N) return;  // the grid is sized for the longest sequence (nothing is allocated yet)
     set_up();
   }
+  // The Q tiles are requested by the thread that initialised their barrier, before the CTA-wide barrier below: the load
+  // travels while tensor memory is being allocated and the history length is fetched.
+  if (tid == 0) {
+    mbar_arrive_expect_tx(q_full, NQ * kTileBytes);
+    for (int q = 0; q < NQ; ++q)
+      for (int kb = 0; kb < kBlocks; ++kb)
+        tma_load_4d(sQ + q * kTileBytes + kb * kBlockBytes, &tm_q, kb * 64, h0 + q * kHeadStep, row0 + t0 + q * kRowStep, tma_seq, q_full);
+  }
   int H = p.hist_lens[s];
   if (H < 0 || p.num_pages <= 0) H = 0;
   {
@@ -462,12 +470,6 @@ __global__ void __launch_bounds__(64 + 128 * NQ, 1)
   if (warp == 0) {
     // =============================== producer ===============================
     int ok = 1;
-    if (lane == 0) {
-      mbar_arrive_expect_tx(q_full, NQ * kTileBytes);
-      for (int q = 0; q < NQ; ++q)
-        for (int kb = 0; kb < kBlocks; ++kb)
-          tma_load_4d(sQ + q * kTileBytes + kb * kBlockBytes, &tm_q, kb * 64, h0 + q * kHeadStep, row0 + t0 + q * kRowStep, tma_seq, q_full);
-    }
     // Key tile j lives in ring stage j % ST; its full / empty barriers are those of index j & 1, used for the
     // (j >> 1)-th time (two barriers per kind even when the ring has one stage, so that nobody ever waits on a barrier
     // that may be more than one phase away from the one it names - a parity wait cannot tell phases two apart).
