@@ -202,8 +202,10 @@ def build_decode(cfg, device, seed, hkv_local=None):
                 alg_bytes=alg_bytes, tokens=cfg["S"], hq=hq_local, hkv=hkv, lens_cpu=lens, partition_pages=pp)
 
 
-def build_prefill(cfg, device, seed, seqs=None):
-    tpp, d, hq, hkv, n = cfg["tpp"], cfg["d"], cfg["hq"], cfg["hkv"], cfg["n"]
+def build_prefill(cfg, device, seed, seqs=None, hkv_local=None):
+    tpp, d, n = cfg["tpp"], cfg["d"], cfg["n"]
+    hkv = hkv_local or cfg["hkv"]            # kv-head sharded: this GPU's kv heads and their query heads, every sequence
+    hq = cfg["hq"] * hkv // cfg["hkv"]
     hist_all = make_lengths(seed, cfg["S"], cfg["hlo"], cfg["hhi"])
     idx = list(range(cfg["S"])) if seqs is None else seqs
     hist = hist_all[idx]
@@ -231,6 +233,7 @@ def build_prefill(cfg, device, seed, seqs=None):
     data["flops"] = 4 * hq * d * sum(int(c) * int(h) + int(c) * (int(c) + 1) // 2 for c, h in zip(counts, hist))
     data["tokens"] = T
     data["hist_cpu"] = hist
+    data["hq"] = hq
     return data
 
 
@@ -579,8 +582,14 @@ def prepare(name, env, pal, peaks, args, force_single=False):
         w.data = data
         w.graph = bool(ctx) and not args.no_cuda_graph
     elif kind == "prefill":
-        seqs = None
-        if world > 1:
+        seqs, hkv_local = None, None
+        if world > 1 and cfg["hkv"] % world == 0:
+            # every GPU does the same work (its share of the heads of every sequence), so no GPU waits for the one that
+            # drew the long sequences
+            hkv_local = cfg["hkv"] // world
+            w.scaling = "strong"
+            w.extra_cfg["parallelism"] = f"kv-head sharded x{world}, no collective"
+        elif world > 1:
             from proxy_attention_lab_b200.sharding import partition_sequences
 
             hist_all = make_lengths(0, cfg["S"], cfg["hlo"], cfg["hhi"])
@@ -589,7 +598,7 @@ def prepare(name, env, pal, peaks, args, force_single=False):
             seqs = partition_sequences(work, world)[rank] or [rank % cfg["S"]]
             w.scaling = "strong"
             w.extra_cfg["parallelism"] = f"sequence sharded x{world} (balanced by attention work), no collective"
-        data = build_prefill(cfg, device, seed=0, seqs=seqs)
+        data = build_prefill(cfg, device, seed=0, seqs=seqs, hkv_local=hkv_local)
 
         def prefill_call(q, k, v, table, hist, cu=None):
             if cu is None:
@@ -599,7 +608,7 @@ def prepare(name, env, pal, peaks, args, force_single=False):
 
         w.step = lambda: prefill_call(data["q"], data["k"], data["v"], data["table"], data["hist"], data.get("cu"))
         host = {k: data[k].cpu().pin_memory() for k in ("q", "k", "v", "table", "hist") + (("cu",) if "cu" in data else ())}
-        out_host = torch.empty((data["tokens"] * cfg["hq"], cfg["d"]), dtype=torch.bfloat16).pin_memory()
+        out_host = torch.empty((data["tokens"] * data["hq"], cfg["d"]), dtype=torch.bfloat16).pin_memory()
         w.pipe = HostPipeline(host, lambda d: prefill_call(d["q"], d["k"], d["v"], d["table"], d["hist"], d.get("cu")), out_host, device)
         w.h2d = sum(t.numel() * t.element_size() for t in host.values())
         w.d2h = out_host.numel() * 2
@@ -610,7 +619,7 @@ def prepare(name, env, pal, peaks, args, force_single=False):
         w.peak = None  # chosen by the length of the timed block (burst or sustained figure)
         w.l2_note = "Q/K/V/out of a step total ~0.4 GB (> 126 MB L2)"
         w.tokens = data["tokens"]
-        w.tokens_are_global = False
+        w.tokens_are_global = hkv_local is not None  # every GPU sees all tokens, for its own heads
         w.data = data
         w.graph = False
     else:

@@ -19,7 +19,7 @@ CSRC = HERE / "csrc"
 LIB = HERE / "libpal_b200.so"
 OBJ_DIR = HERE / "build"
 SOURCES = ["api.cu", "fill_kv_pages.cu", "decode.cu", "prefill_mma.cu", "prefill_tcgen05.cu", "prefill_tcgen05_d64_t16.cu", "prefill_tcgen05_d64_t32.cu", "prefill_tcgen05_d128_t16.cu",
-           "prefill_tcgen05_d128_t32.cu", "prefill_tcgen05_d256_t16.cu", "prefill_tcgen05_d256_t32.cu", "decode_static.cu", "decode_exchange.cu"]
+           "prefill_tcgen05_d128_t32.cu", "prefill_tcgen05_d256_t16.cu", "prefill_tcgen05_d256_t32.cu", "prefill_tcgen05_pair_d128.cu", "prefill_tcgen05_pair_d256.cu", "decode_static.cu", "decode_exchange.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",
     "-O3", "-std=c++17", "-lineinfo",

@@ -555,9 +555,13 @@ static int prefill_common(const char* what, const void* q_prompt, const void* k_
   a.workspace = workspace;
   a.workspace_bytes = workspace_bytes;
   const bool tc_ok = prefill_tcgen05_supports(head_dim, tokens_per_page);
-  if (impl < 0 || impl > 3) {
-    set_error("%s: impl must be 0 (auto), 1 (mma.sync), 2 (tcgen05) or 3 (tcgen05, one accumulator tile per CTA)", what);
+  if (impl < 0 || impl > 4) {
+    set_error("%s: impl must be 0 (auto), 1 (mma.sync), 2 (tcgen05), 3 (tcgen05, one accumulator tile per CTA) or 4 (tcgen05, two CTAs per MMA)", what);
     return PAL_ERR_BAD_ARG;
+  }
+  if (impl == 4 && !prefill_tcgen05_pair_supports(head_dim, tokens_per_page, num_q_heads, num_kv_heads)) {
+    set_error("%s: the two-CTA tcgen05 kernel covers head_dim 128 / 256 with tokens_per_page 16 / 32 and an even number of query heads per kv head", what);
+    return PAL_ERR_UNSUPPORTED;
   }
   if (impl >= 2 && !tc_ok) {
     set_error("%s: the tcgen05 kernel covers head_dim in {64, 128, 256} with tokens_per_page in {16, 32}", what);

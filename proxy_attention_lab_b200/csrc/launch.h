@@ -159,6 +159,7 @@ int launch_exchange_combine(const ExchangeArgs& a, cudaStream_t stream);
 int launch_prefill_mma(const PrefillArgs& a, cudaStream_t stream);
 int launch_prefill_tcgen05(const PrefillArgs& a, cudaStream_t stream);
 bool prefill_tcgen05_supports(int head_dim, int tokens_per_page);
+bool prefill_tcgen05_pair_supports(int head_dim, int tokens_per_page, int num_q_heads, int num_kv_heads);
 
 size_t decode_workspace_bytes(int num_seqs, int num_q_heads, int num_kv_heads, int head_dim, int tokens_per_page,
                               int max_pages_per_seq, int partition_pages);

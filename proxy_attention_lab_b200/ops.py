@@ -453,7 +453,7 @@ def lse_combine_packed(packed, out_dtype=torch.bfloat16, *, out_shape=None, stre
 # ---------------------------------------------------------------------------------------------
 # paged_attention_prefill (src/proxy_attention_lab/ops.py:87-130, src/pal_core/src/ops.cpp:110-185)
 # ---------------------------------------------------------------------------------------------
-PREFILL_IMPL = {"auto": 0, "mma": 1, "tcgen05": 2, "tcgen05_single": 3}
+PREFILL_IMPL = {"auto": 0, "mma": 1, "tcgen05": 2, "tcgen05_single": 3, "tcgen05_pair": 4}
 
 
 def _prefill_shapes(q_prompt, k_prompt, v_prompt, k_cache_paged, v_cache_paged, page_table, context_len_arr):

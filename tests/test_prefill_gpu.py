@@ -161,3 +161,40 @@ def test_sequences_are_processed_in_order_of_work(pal, cuda, impl, num_seqs):
     hist[-1] = hist[0]
     case = make_prefill_case(400 + num_seqs, hist, 64, 4, 2, 128, dtype=torch.bfloat16, poison_unused=True)
     check(pal, cuda, case, impl)
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("d", [128, 256])
+@pytest.mark.parametrize("tpp", [16, 32])
+def test_two_cta_kernel(pal, cuda, dtype, d, tpp):
+    """The cta_group::2 form (two CTAs per MMA, each loading half of every K / V tile): histories that end inside a page and
+    inside a tile, none, shorter than the 64 keys of CTA 0's half, just past them; several query tiles; groups of 2 and 4
+    query heads per kv head; unused pool slots poisoned."""
+    for hq, hkv, hist, n in ((4, 2, [700, 0, 131], 300), (8, 2, [40, 64, 65, 2000], 130)):
+        case = make_prefill_case(50 + d + tpp, hist, n, hq, hkv, d, tpp=tpp, dtype=dtype, poison_unused=True)
+        check(pal, cuda, case, "tcgen05_pair")
+
+
+def test_two_cta_kernel_serves_head_dim_256_by_default(pal, cuda):
+    """With head_dim 256 and an even group the launcher's choice is the two-CTA form (bit-equal to asking for it); an odd
+    group, or impl="tcgen05_single", runs the one-CTA kernel; the two agree within the tolerance of either."""
+    case = make_prefill_case(61, [300, 17], 200, 4, 2, 256, dtype=torch.bfloat16)
+    auto = run_prefill(pal, case, cuda, impl="tcgen05")
+    assert torch.equal(auto, run_prefill(pal, case, cuda, impl="tcgen05_pair"))
+    assert torch.equal(auto, run_prefill(pal, case, cuda))
+    single = run_prefill(pal, case, cuda, impl="tcgen05_single")
+    assert max_abs(auto, single) <= 2 * TOL + 2.0 ** -7 * single.float().abs().max().item()
+    odd = make_prefill_case(62, [300, 17], 200, 3, 3, 256, dtype=torch.bfloat16)
+    check(pal, cuda, odd, "tcgen05")
+    t = to_dev(odd, cuda)
+    with pytest.raises(RuntimeError):
+        pal.paged_attention_prefill(t["q"], t["k_new"], t["v_new"], t["k_pool"], t["v_pool"], t["page_table"], t["hist"], impl="tcgen05_pair")
+
+
+@pytest.mark.parametrize("d", [128, 256])
+def test_two_cta_kernel_determinism_and_status(pal, cuda, d):
+    case = make_prefill_case(63, [1024, 0], 384, 8, 2, d, dtype=torch.bfloat16)
+    a = run_prefill(pal, case, cuda, impl="tcgen05_pair")
+    b = run_prefill(pal, case, cuda, impl="tcgen05_pair")
+    assert torch.equal(a, b)
+    pal.check_status()

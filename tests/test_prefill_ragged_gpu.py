@@ -70,7 +70,7 @@ def test_neighbours_values_cannot_leak_into_a_short_sequence(pal, cuda):
             if s != victim:
                 v[cu[s]:cu[s + 1]] = float("nan")
         poisoned["v"] = v
-        for impl in ("mma", "tcgen05", "tcgen05_single"):
+        for impl in ("mma", "tcgen05", "tcgen05_single", "tcgen05_pair"):
             out = run(pal, cuda, poisoned, impl=impl).reshape(-1, 4, 128)
             got = out[cu[victim]:cu[victim + 1]]
             assert torch.isfinite(got.float()).all(), (victim, impl)
@@ -104,6 +104,15 @@ def test_ragged_batches_ordered_by_work(pal, cuda, impl, num_seqs):
     counts[1] = 1
     c = make_ragged_case(600 + num_seqs, hist, counts, 4, 2, 128, poison_unused=True)
     check(pal, cuda, c, impl)
+
+
+@pytest.mark.parametrize("d,tpp", [(128, 16), (128, 32), (256, 16), (256, 32)])
+def test_ragged_batches_on_the_two_cta_kernel(pal, cuda, d, tpp):
+    """Counts around the tile edges, single tokens, an empty sequence, foreign rows after a short sequence's last tile
+    (their V rows are zero-filled by each CTA for its half of the head dimension)."""
+    counts = [1, 140, 0, 64, 129, 5, 128, 300]
+    hist = [100, 0, 50, 129, 16, 300, 63, 1000]
+    check(pal, cuda, make_ragged_case(31, hist, counts, 4, 2, d, tpp=tpp, poison_unused=True), "tcgen05_pair")
 
 
 @pytest.mark.parametrize("impl", IMPLS)
