@@ -262,8 +262,13 @@ size_t pal_prefill_workspace_bytes(int num_seqs, int tokens_per_seq, int num_q_h
  * history_lens[s] tokens of history are read from the pages; out [S*N*Hq, D], row
  * (s*N + i)*Hq + h.  Query i sees all history tokens and new tokens 0..i.
  * dtype may carry PAL_OUT_F32 (float32 output).
- * impl: 0 = let the launcher choose, 1 = mma.sync kernel (every supported shape),
- * 2 = tcgen05/TMEM kernel (D = 128, TPP = 16 only; PAL_ERR_UNSUPPORTED otherwise). */
+ * impl: 0 = let the launcher choose (the tcgen05 kernel where it covers the shape and tokens_per_seq >= 64),
+ * 1 = mma.sync kernel (every supported shape),
+ * 2 = tcgen05/TMEM kernel (head_dim 64 / 128 / 256 with tokens_per_page 16 / 32; PAL_ERR_UNSUPPORTED otherwise),
+ *     in the form the launcher prefers for the shape,
+ * 3 = tcgen05, one accumulator tile per CTA with S double-buffered,
+ * 4 = tcgen05, two CTAs per MMA (cta_group::2; head_dim 128 / 256 and an even number of query heads per kv head,
+ *     PAL_ERR_UNSUPPORTED otherwise; what 0 and 2 choose for head_dim 256 with even groups). */
 int pal_paged_attention_prefill(const void* q_prompt, const void* k_prompt, const void* v_prompt,
                                 const void* k_pool, const void* v_pool, const void* page_table,
                                 const int32_t* history_lens, void* out, int num_seqs,

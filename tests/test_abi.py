@@ -161,3 +161,24 @@ def test_auto_partition_size_gives_the_memory_system_enough_ctas():
     assert ops.resolve_partition_pages(None, 64, 32, 8, 128, 16, 512) == 512
     assert ops.resolve_partition_pages(37, 64, 32, 8, 128, 16, 512) == 37
     assert ops.resolve_partition_pages(-1, 8, 8, 1, 128, 16, 8192) == f(8, 8, 1, 128, 16, 8192)
+
+
+def test_prefill_impl_argument_is_validated_before_anything_runs():
+    """impl 0..4 exist; 4 (two CTAs per MMA) needs head_dim 128 / 256 and an even number of query heads per kv head.
+    The buffers are host memory that is never touched: every call fails in validation."""
+    from proxy_attention_lab_b200 import _lib
+
+    lib = _lib.lib
+    raw = ctypes.create_string_buffer(4096)
+    base = (ctypes.addressof(raw) + 255) & ~255  # 256-byte aligned, as the workspace must be
+    buf = ctypes.c_void_p(base)
+
+    def call(hq, hkv, d, impl):
+        return lib.pal_paged_attention_prefill(buf, buf, buf, buf, buf, buf, ctypes.cast(buf, ctypes.POINTER(ctypes.c_int32)), buf, 1, 64,
+                                               hq, hkv, d, 16, 1, 1, 0.0, 1, impl, buf, 256, None)
+
+    assert call(4, 2, 128, 5) == _lib.PAL_ERR_BAD_ARG and "impl" in _lib.last_error()
+    assert call(4, 2, 128, -1) == _lib.PAL_ERR_BAD_ARG
+    assert call(4, 2, 64, 4) == _lib.PAL_ERR_UNSUPPORTED and "two-CTA" in _lib.last_error()
+    assert call(3, 3, 128, 4) == _lib.PAL_ERR_UNSUPPORTED
+    assert call(4, 2, 96, 2) == _lib.PAL_ERR_UNSUPPORTED
