@@ -69,6 +69,12 @@ WORKLOADS = {
                           desc="reduced chunked prefill for profiler captures: 2 x 1024 new tokens, history U[0,2048], 32q/8kv heads, D=128, bf16, TPP=16"),
     "prefill_wave": dict(kind="prefill", S=4, n=2048, hlo=2048, hhi=2048, hq=32, hkv=8, d=128, tpp=16,
                          desc="one full wave of prefill CTAs for profiler captures: 4 x 2048 new tokens, history 2048, 32q/8kv heads, D=128, bf16, TPP=16"),
+    "prefill_d256": dict(kind="prefill", S=8, n=2048, hlo=0, hhi=4096, hq=32, hkv=8, d=256, tpp=16,
+                         desc="chunked causal prefill at head_dim 256 (the two-CTA tcgen05 kernel): 8 x 2048 new tokens, history U[0,4096], "
+                              "32q/8kv heads, D=256, bf16, TPP=16"),
+    "prefill_d256_wave": dict(kind="prefill", S=2, n=2048, hlo=2048, hhi=2048, hq=32, hkv=8, d=256, tpp=16,
+                              desc="full waves of two-CTA prefill clusters for profiler captures: 2 x 2048 new tokens, history 2048, 32q/8kv heads, "
+                                   "D=256, bf16, TPP=16"),
     "prefill_ragged": dict(kind="prefill", S=8, n=2048, nlo=128, hlo=0, hhi=4096, hq=32, hkv=8, d=128, tpp=16,
                            desc="ragged chunked causal prefill (paged_attention_prefill_ragged): 8 sequences with U[128,2048] new tokens each, "
                                 "history U[0,4096], 32q/8kv heads, D=128, bf16, TPP=16"),
@@ -745,7 +751,7 @@ def measure(w, env, peaks, steps, warmup, blocks, e2e=True):
 # 0.904 x its algorithmic bytes (captured on the reduced case; the traffic grows with the tokens).
 PROFILED_TRAFFIC = {"decode_8b": 1.3866e9, "decode_8b_append": 1.3889e9}
 
-EXTRA_SINGLE = ["prefill_8b", "decode_70b", "decode_70b_auto", "fill", "fill_append"]
+EXTRA_SINGLE = ["prefill_8b", "prefill_d256", "decode_70b", "decode_70b_auto", "fill", "fill_append"]
 EXTRA_MULTI = ["decode_70b", "decode_70b_auto", "decode_70b_ctx", "decode_70b_ctx_fused", "decode_70b_ctx_fused_auto", "prefill_8b"]
 
 
