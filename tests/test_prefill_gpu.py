@@ -198,3 +198,14 @@ def test_two_cta_kernel_determinism_and_status(pal, cuda, d):
     b = run_prefill(pal, case, cuda, impl="tcgen05_pair")
     assert torch.equal(a, b)
     pal.check_status()
+
+
+@pytest.mark.parametrize("d,dtype", [(256, torch.bfloat16), (256, torch.float16), (128, torch.bfloat16)])
+def test_two_cta_kernel_equals_the_one_cta_kernel_bit_for_bit(pal, cuda, d, dtype):
+    """Both kernels multiply the same tiles in the same order (M = 256 across two CTAs against M = 128 in one) and share the
+    softmax code, so on a problem of several waves - long and short histories, 16 query tiles - every output bit agrees."""
+    case = make_prefill_case(71, [3000, 0, 517, 2048], 2048, 8, 4, d, dtype=dtype)
+    pair = run_prefill(pal, case, cuda, impl="tcgen05_pair")
+    single = run_prefill(pal, case, cuda, impl="tcgen05_single")
+    assert torch.equal(pair, single)
+    pal.check_status()
