@@ -264,7 +264,7 @@ size_t pal_prefill_workspace_bytes(int num_seqs, int tokens_per_seq, int num_q_h
  * dtype may carry PAL_OUT_F32 (float32 output).
  * impl: 0 = let the launcher choose (the tcgen05 kernel where it covers the shape and tokens_per_seq >= 64),
  * 1 = mma.sync kernel (every supported shape),
- * 2 = tcgen05/TMEM kernel (head_dim 64 / 128 / 256 with tokens_per_page 16 / 32; PAL_ERR_UNSUPPORTED otherwise),
+ * 2 = tcgen05/TMEM kernel (head_dim 32 / 64 / 80 / 96 / 128 / 256 with tokens_per_page 16 / 32: every supported shape),
  *     in the form the launcher prefers for the shape,
  * 3 = tcgen05, one accumulator tile per CTA with S double-buffered,
  * 4 = tcgen05, two CTAs per MMA (cta_group::2; head_dim 128 / 256 and an even number of query heads per kv head,

@@ -18,7 +18,7 @@ HERE = Path(__file__).resolve().parent
 CSRC = HERE / "csrc"
 LIB = HERE / "libpal_b200.so"
 OBJ_DIR = HERE / "build"
-SOURCES = ["api.cu", "fill_kv_pages.cu", "decode.cu", "prefill_mma.cu", "prefill_tcgen05.cu", "prefill_tcgen05_d64_t16.cu", "prefill_tcgen05_d64_t32.cu", "prefill_tcgen05_d128_t16.cu",
+SOURCES = ["api.cu", "fill_kv_pages.cu", "decode.cu", "prefill_mma.cu", "prefill_tcgen05.cu", "prefill_tcgen05_d32_t16.cu", "prefill_tcgen05_d32_t32.cu", "prefill_tcgen05_d80_t16.cu", "prefill_tcgen05_d80_t32.cu", "prefill_tcgen05_d96_t16.cu", "prefill_tcgen05_d96_t32.cu", "prefill_tcgen05_d64_t16.cu", "prefill_tcgen05_d64_t32.cu", "prefill_tcgen05_d128_t16.cu",
            "prefill_tcgen05_d128_t32.cu", "prefill_tcgen05_d256_t16.cu", "prefill_tcgen05_d256_t32.cu", "prefill_tcgen05_pair_d128.cu", "prefill_tcgen05_pair_d256.cu", "decode_static.cu", "decode_exchange.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",

@@ -564,7 +564,7 @@ static int prefill_common(const char* what, const void* q_prompt, const void* k_
     return PAL_ERR_UNSUPPORTED;
   }
   if (impl >= 2 && !tc_ok) {
-    set_error("%s: the tcgen05 kernel covers head_dim in {64, 128, 256} with tokens_per_page in {16, 32}", what);
+    set_error("%s: the tcgen05 kernel covers head_dim in {32, 64, 80, 96, 128, 256} with tokens_per_page in {16, 32}", what);
     return PAL_ERR_UNSUPPORTED;
   }
   const bool use_tc = impl >= 2 || (impl == 0 && tc_ok && tokens_per_seq >= 64);

@@ -1,10 +1,10 @@
-// Dispatch of the tcgen05 prefill kernel over its instantiations (head_dim 64 / 128 / 256 x tokens_per_page 16 / 32);
+// Dispatch of the tcgen05 prefill kernel over its instantiations (head_dim 32 / 64 / 80 / 96 / 128 / 256 x tokens_per_page 16 / 32);
 // the kernel itself is in prefill_tcgen05.cuh, one translation unit per shape.
 #include "launch.h"
 
 namespace pal {
 
-#define PAL_TC_SHAPES(X) X(64, 16) X(64, 32) X(128, 16) X(128, 32) X(256, 16) X(256, 32)
+#define PAL_TC_SHAPES(X) X(32, 16) X(32, 32) X(64, 16) X(64, 32) X(80, 16) X(80, 32) X(96, 16) X(96, 32) X(128, 16) X(128, 32) X(256, 16) X(256, 32)
 #define PAL_TC_DECLARE(DD, TT) int launch_prefill_tcgen05_d##DD##_t##TT(const PrefillArgs& a, cudaStream_t stream);
 PAL_TC_SHAPES(PAL_TC_DECLARE)
 #undef PAL_TC_DECLARE
@@ -39,7 +39,7 @@ int launch_prefill_tcgen05(const PrefillArgs& a, cudaStream_t stream) {
   if (a.head_dim == DD && a.tokens_per_page == TT) return launch_prefill_tcgen05_d##DD##_t##TT(a, stream);
   PAL_TC_SHAPES(PAL_TC_CALL)
 #undef PAL_TC_CALL
-  set_error("paged_attention_prefill: the tcgen05 kernel covers head_dim in {64, 128, 256} with tokens_per_page in {16, 32}");
+  set_error("paged_attention_prefill: the tcgen05 kernel covers head_dim in {32, 64, 80, 96, 128, 256} with tokens_per_page in {16, 32}");
   return -2;
 }
 

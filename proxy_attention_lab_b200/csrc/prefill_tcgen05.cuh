@@ -1,11 +1,11 @@
 // Paged-attention prefill on the 5th-generation tensor cores: tcgen05.mma with TMEM accumulators,
-// operands staged by TMA / bulk copies, for head_dim 64 / 128 / 256 and tokens_per_page 16 / 32.
+// operands staged by TMA / bulk copies, for head_dim 32 / 64 / 80 / 96 / 128 / 256 and tokens_per_page 16 / 32.
 //
 // Replaces pal_paged_attention_prefill (src/pal_core/kernels/paged_attention/prefill/
 // paged_attention_prefill.h.metal:28-389), which handles one key per iteration per simdgroup with
 // scalar FMAs, and its launcher (src/pal_core/src/paged_attention_prefill_primitive.cpp:63-167); the
-// instantiation grid is the reference's (paged_attention_kernels.metal:111-131) for the head dims that
-// are whole 64-element swizzle blocks.
+// instantiation grid is the reference's (paged_attention_kernels.metal:111-131): head dims that are not whole
+// 64-element swizzle blocks (32, 80, 96) use tiles padded to the next one, whose padding is neither computed on nor stored.
 //
 // One CTA owns NQ (1 or 2) accumulator tiles of M = 128 rows that read the same K / V tiles: 128 consecutive new
 // tokens of two query heads that share a kv head, or - when the heads per kv head are odd in number, e.g. one -
@@ -72,19 +72,24 @@ constexpr float kRescaleThreshold = 8.0f;       // log2 units
 template <int D_, int TPP_, int NQ_, int SBUF_>
 struct TcCfg {
   static constexpr int D = D_, TPP = TPP_, NQ = NQ_, SBUF = SBUF_;
-  static_assert(D == 64 || D == 128 || D == 256, "head_dim must be 64, 128 or 256");
+  static_assert(D == 32 || D == 64 || D == 80 || D == 96 || D == 128 || D == 256, "head_dim must be 32, 64, 80, 96, 128 or 256");
+  // Shared-memory tiles are laid out for the head dim rounded up to whole 64-element swizzle blocks (32 -> 64; 80, 96 ->
+  // 128).  The tensor maps carry the real head dim, so the columns past it arrive as zeros and leave clipped; the MMAs
+  // only step over the real ones (K steps of 16 for QK^T, N = head_dim for PV), so nothing is computed on the padding.
+  static constexpr int DP = (D + 63) / 64 * 64;
+  static constexpr int kOChunk = D % 32 == 0 ? 32 : 16;  // columns of O moved per tcgen05.ld / st in the rescale and epilogue
   static_assert(TPP == 16 || TPP == 32, "tokens_per_page must be 16 or 32");
   static_assert(SBUF == 1 || (SBUF == 2 && NQ == 1), "S is double-buffered only with one accumulator tile per CTA");
-  static constexpr int kBlocks = D / 64;              // 64-element blocks of a row
+  static constexpr int kBlocks = DP / 64;             // 64-element blocks of a (padded) row
   static constexpr int kPagesPerTile = kTile / TPP;
   static constexpr int kPageBytes = D * TPP * 2;
-  static constexpr int kTileBytes = kTile * D * 2;
+  static constexpr int kTileBytes = kTile * DP * 2;   // a Q tile, and a ring stage of K or V
   static constexpr int kStages = D <= 128 ? 2 : 1;    // K ring and V ring depth (head_dim 256: 64 KB per tile)
   static constexpr int kChunkBytes = kTile * 16;      // one 8-element chunk of all 128 tokens of a history K tile
   // TMEM columns
   static constexpr int kSCols = NQ * SBUF * kTile;
   static constexpr int kOBase = kSCols;
-  static_assert(kSCols + NQ * D <= 512, "TMEM holds 512 columns");
+  static_assert(kSCols + NQ * DP <= 512, "TMEM holds 512 columns");
   // shared memory
   static constexpr int kQ = 0;
   static constexpr int kK = NQ * kTileBytes;
@@ -206,6 +211,10 @@ __device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16
       "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
       : "memory");
 }
+__device__ __forceinline__ void tmem_ldw(uint32_t taddr, uint32_t (&r)[32]) { tmem_ld32(taddr, r); }
+__device__ __forceinline__ void tmem_ldw(uint32_t taddr, uint32_t (&r)[16]) { tmem_ld16(taddr, r); }
+__device__ __forceinline__ void tmem_stw(uint32_t taddr, const uint32_t (&r)[32]) { tmem_st32(taddr, r); }
+__device__ __forceinline__ void tmem_stw(uint32_t taddr, const uint32_t (&r)[16]) { tmem_st16(taddr, r); }
 __device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void fence_proxy_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
@@ -369,7 +378,7 @@ __global__ void __launch_bounds__(64 + 128 * NQ, 1)
                            const __grid_constant__ CUtensorMap tm_kpool, const __grid_constant__ CUtensorMap tm_out) {
   using C = TcCfg<D, TPP, NQ, SBUF>;
   constexpr int kBlocks = C::kBlocks, kPagesPerTile = C::kPagesPerTile, kPageBytes = C::kPageBytes, kTileBytes = C::kTileBytes;
-  constexpr int ST = C::kStages;
+  constexpr int ST = C::kStages, kOC = C::kOChunk;
   extern __shared__ unsigned char smem_raw[];
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   unsigned char* sQ = smem + C::kQ;
@@ -598,7 +607,7 @@ __global__ void __launch_bounds__(64 + 128 * NQ, 1)
       auto issue_pv = [&](int q, int j) {
         if (!elect_one()) return;
         const int st = j % ST;
-        const uint32_t d_tmem = tmem_base + C::kOBase + q * D;
+        const uint32_t d_tmem = tmem_base + C::kOBase + q * C::DP;
         const uint32_t a_tmem = tmem_base + s_index(q, j) * kTile;  // P over the first 64 columns of the S tile
         for (int part = 0; part < (split_p ? 2 : 1); ++part) {  // part 1: the residual of P, 64 columns on
           const uint32_t a_part = a_tmem + part * 64;
@@ -676,7 +685,7 @@ __global__ void __launch_bounds__(64 + 128 * NQ, 1)
     const int lane_group = warp & 3;            // the TMEM sub-partition this warp may touch
     const int row = lane_group * 32 + lane;     // row of the 128-row tile = TMEM lane
     const uint32_t lane_addr = (uint32_t)(lane_group * 32) << 16;
-    const uint32_t tO = tmem_base + lane_addr + C::kOBase + q * D;
+    const uint32_t tO = tmem_base + lane_addr + C::kOBase + q * C::DP;
     const int t0q = t0 + q * kRowStep;          // first query token of this accumulator tile
     const int diag = t0q / kTile;               // its diagonal key tile among the new tokens
     const int qi = t0q + row;                   // index of this row's query token in its sequence
@@ -715,13 +724,13 @@ __global__ void __launch_bounds__(64 + 128 * NQ, 1)
         tc_fence_after();
         const float f = fast_exp2(m_used - m_new);
 #pragma unroll
-        for (int c4 = 0; c4 < D / 32; ++c4) {
-          uint32_t v[32];
-          tmem_ld32(tO + c4 * 32, v);
+        for (int c4 = 0; c4 < D / kOC; ++c4) {
+          uint32_t v[kOC];
+          tmem_ldw(tO + c4 * kOC, v);
           tmem_wait_ld();
 #pragma unroll
-          for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * f);
-          tmem_st32(tO + c4 * 32, v);
+          for (int i = 0; i < kOC; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * f);
+          tmem_stw(tO + c4 * kOC, v);
         }
         tmem_wait_st();
         l_run *= f;
@@ -790,33 +799,33 @@ __global__ void __launch_bounds__(64 + 128 * NQ, 1)
       T* orow = static_cast<T*>(p.out) + out_off;
       unsigned char* stage = sQ + q * kTileBytes + row * 128;
 #pragma unroll
-      for (int c4 = 0; c4 < D / 32; ++c4) {
-        uint32_t v[32];
-        tmem_ld32(tO + c4 * 32, v);
+      for (int c4 = 0; c4 < D / kOC; ++c4) {
+        uint32_t v[kOC];
+        tmem_ldw(tO + c4 * kOC, v);
         tmem_wait_ld();
         if (p.out_f32) {
           if (qi < N) {
-            float4* o32 = reinterpret_cast<float4*>(static_cast<float*>(p.out) + out_off + c4 * 32);
+            float4* o32 = reinterpret_cast<float4*>(static_cast<float*>(p.out) + out_off + c4 * kOC);
 #pragma unroll
-            for (int i = 0; i < 8; ++i)
+            for (int i = 0; i < kOC / 4; ++i)
               o32[i] = make_float4(__uint_as_float(v[4 * i]) * inv, __uint_as_float(v[4 * i + 1]) * inv,
                                    __uint_as_float(v[4 * i + 2]) * inv, __uint_as_float(v[4 * i + 3]) * inv);
           }
           continue;
         }
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
+        for (int i = 0; i < kOC / 8; ++i) {
           uint4 w;
           w.x = Mma16816<T>::pack(__uint_as_float(v[8 * i + 0]) * inv, __uint_as_float(v[8 * i + 1]) * inv);
           w.y = Mma16816<T>::pack(__uint_as_float(v[8 * i + 2]) * inv, __uint_as_float(v[8 * i + 3]) * inv);
           w.z = Mma16816<T>::pack(__uint_as_float(v[8 * i + 4]) * inv, __uint_as_float(v[8 * i + 5]) * inv);
           w.w = Mma16816<T>::pack(__uint_as_float(v[8 * i + 6]) * inv, __uint_as_float(v[8 * i + 7]) * inv);
+          // 16-byte chunk c of the row: 64-element block c / 8, chunk c % 8 xor-swizzled with the row
+          const int c = (kOC / 8) * c4 + i;
           if (tma_out) {
-            // 16-byte chunk c = 4 c4 + i of the row: 64-element block c / 8, chunk c % 8 xor-swizzled with the row
-            const int c = 4 * c4 + i;
             *reinterpret_cast<uint4*>(stage + (c >> 3) * kBlockBytes + (((c & 7) ^ (row & 7)) << 4)) = w;
           } else if (qi < N) {
-            *reinterpret_cast<uint4*>(orow + c4 * 32 + i * 8) = w;
+            *reinterpret_cast<uint4*>(orow + c * 8) = w;
           }
         }
       }

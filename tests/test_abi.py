@@ -181,4 +181,4 @@ def test_prefill_impl_argument_is_validated_before_anything_runs():
     assert call(4, 2, 128, -1) == _lib.PAL_ERR_BAD_ARG
     assert call(4, 2, 64, 4) == _lib.PAL_ERR_UNSUPPORTED and "two-CTA" in _lib.last_error()
     assert call(3, 3, 128, 4) == _lib.PAL_ERR_UNSUPPORTED
-    assert call(4, 2, 96, 2) == _lib.PAL_ERR_UNSUPPORTED
+    assert call(4, 2, 48, 2) == _lib.PAL_ERR_UNSUPPORTED

@@ -19,8 +19,9 @@ def run_prefill(pal, case, device, **kw):
 
 
 def supported(impl, d, tpp=16):
-    """The tcgen05 kernel covers the head dims that are whole 64-element blocks; the mma.sync kernel every shape."""
-    return impl == "mma" or (d in (64, 128, 256) and tpp in (16, 32))
+    """Both kernels cover the reference's whole grid: head_dim 32 / 64 / 80 / 96 / 128 / 256 with 16- or 32-token pages (the
+    tcgen05 kernel lays 32, 80 and 96 out in tiles padded to whole 64-element swizzle blocks)."""
+    return d in (32, 64, 80, 96, 128, 256) and tpp in (16, 32)
 
 
 def check(pal, cuda, case, impl):
@@ -65,7 +66,7 @@ def test_head_dims_and_page_sizes(pal, cuda, impl, d, tpp):
 
 @pytest.mark.parametrize("impl", ["tcgen05", "tcgen05_single"])
 @pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
-@pytest.mark.parametrize("d", [64, 128, 256])
+@pytest.mark.parametrize("d", [32, 64, 80, 96, 128, 256])
 @pytest.mark.parametrize("tpp", [16, 32])
 def test_tcgen05_shapes_with_long_history_and_several_tiles(pal, cuda, impl, dtype, d, tpp):
     """Every tcgen05 instantiation over several history tiles (a partial last page, a partial last tile), several query
@@ -125,11 +126,13 @@ def test_tcgen05_matches_mma(pal, cuda, dtype):
     check(pal, cuda, case, "tcgen05")
 
 
-def test_tcgen05_unsupported_shape_raises(pal, cuda):
-    case = make_prefill_case(35, [10], 16, 4, 2, 96, dtype=torch.float16)
+def test_unsupported_head_dim_raises(pal, cuda):
+    """A head_dim outside the reference's grid is refused by either kernel (nothing is launched)."""
+    case = make_prefill_case(35, [10], 16, 4, 2, 48, dtype=torch.float16)
     t = to_dev(case, cuda)
-    with pytest.raises(RuntimeError):
-        pal.paged_attention_prefill(t["q"], t["k_new"], t["v_new"], t["k_pool"], t["v_pool"], t["page_table"], t["hist"], impl="tcgen05")
+    for impl in ("tcgen05", "mma", "auto"):
+        with pytest.raises(RuntimeError):
+            pal.paged_attention_prefill(t["q"], t["k_new"], t["v_new"], t["k_pool"], t["v_pool"], t["page_table"], t["hist"], impl=impl)
 
 
 def test_chunked_prefill_config_reduced(pal, cuda):

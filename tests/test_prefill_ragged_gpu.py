@@ -49,7 +49,7 @@ def test_mixed_counts_around_tile_edges(pal, cuda, impl, dtype):
 
 
 @pytest.mark.parametrize("impl", ["tcgen05", "tcgen05_single"])
-@pytest.mark.parametrize("d,tpp", [(64, 16), (64, 32), (128, 32), (256, 16), (256, 32)])
+@pytest.mark.parametrize("d,tpp", [(32, 16), (32, 32), (64, 16), (64, 32), (80, 16), (80, 32), (96, 16), (96, 32), (128, 32), (256, 16), (256, 32)])
 def test_ragged_batches_on_the_other_tcgen05_shapes(pal, cuda, impl, d, tpp):
     counts = [1, 140, 0, 64, 129, 5]
     hist = [100, 0, 50, 129, 16, 300]
