@@ -262,7 +262,7 @@ size_t pal_prefill_workspace_bytes(int num_seqs, int tokens_per_seq, int num_q_h
  * history_lens[s] tokens of history are read from the pages; out [S*N*Hq, D], row
  * (s*N + i)*Hq + h.  Query i sees all history tokens and new tokens 0..i.
  * dtype may carry PAL_OUT_F32 (float32 output).
- * impl: 0 = let the launcher choose (the tcgen05 kernel where it covers the shape and tokens_per_seq >= 64),
+ * impl: 0 = let the launcher choose (a tcgen05 kernel for every supported shape),
  * 1 = mma.sync kernel (every supported shape),
  * 2 = tcgen05/TMEM kernel (head_dim 32 / 64 / 80 / 96 / 128 / 256 with tokens_per_page 16 / 32: every supported shape),
  *     in the form the launcher prefers for the shape,
