@@ -59,3 +59,22 @@ def test_append_and_prefill_replay(pal, cuda):
     torch.cuda.synchronize()
     assert _bit_equal(out_a.cpu(), pal.paged_attention_decode_append(nk, nv, q, k, v, table, ln).cpu())
     assert _bit_equal(out_p.cpu(), pal.paged_attention_prefill(pq, pk, pv, pkp, pvp, ptab, phist).cpu())
+
+
+def test_two_cta_prefill_replays_from_a_graph(pal, cuda):
+    """The head_dim 256 prefill kernel is launched with a cluster-dimension attribute; a captured launch replays with new
+    inputs like any other."""
+    pc = make_prefill_case(7, [0, 300, 77], 192, 8, 2, 256)
+    pq, pk, pv = pc.q.to(cuda), pc.k_new.to(cuda), pc.v_new.to(cuda)
+    pkp, pvp, ptab, phist = pc.k_pool.to(cuda), pc.v_pool.to(cuda), pc.page_table.to(cuda), pc.hist.to(cuda)
+    pal.paged_attention_prefill(pq, pk, pv, pkp, pvp, ptab, phist)  # warm-up
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        out_p = pal.paged_attention_prefill(pq, pk, pv, pkp, pvp, ptab, phist)
+    pq.copy_(torch.randn_like(pq))
+    phist.copy_(torch.tensor([16, 120, 300], dtype=phist.dtype, device=cuda))
+    graph.replay()
+    torch.cuda.synchronize()
+    assert _bit_equal(out_p.cpu(), pal.paged_attention_prefill(pq, pk, pv, pkp, pvp, ptab, phist).cpu())
+    pal.check_status()
