@@ -267,8 +267,8 @@ size_t pal_prefill_workspace_bytes(int num_seqs, int tokens_per_seq, int num_q_h
  * 2 = tcgen05/TMEM kernel (head_dim 32 / 64 / 80 / 96 / 128 / 256 with tokens_per_page 16 / 32: every supported shape),
  *     in the form the launcher prefers for the shape,
  * 3 = tcgen05, one accumulator tile per CTA with S double-buffered,
- * 4 = tcgen05, two CTAs per MMA (cta_group::2; head_dim 128 / 256 and an even number of query heads per kv head,
- *     PAL_ERR_UNSUPPORTED otherwise; what 0 and 2 choose for head_dim 256 with even groups). */
+ * 4 = tcgen05, two CTAs per MMA (cta_group::2; head_dim 256, and head_dim 128 with an even number of query heads per
+ *     kv head; PAL_ERR_UNSUPPORTED otherwise; what 0 and 2 choose for head_dim 256). */
 int pal_paged_attention_prefill(const void* q_prompt, const void* k_prompt, const void* v_prompt,
                                 const void* k_pool, const void* v_pool, const void* page_table,
                                 const int32_t* history_lens, void* out, int num_seqs,

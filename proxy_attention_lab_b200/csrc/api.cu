@@ -560,7 +560,7 @@ static int prefill_common(const char* what, const void* q_prompt, const void* k_
     return PAL_ERR_BAD_ARG;
   }
   if (impl == 4 && !prefill_tcgen05_pair_supports(head_dim, tokens_per_page, num_q_heads, num_kv_heads)) {
-    set_error("%s: the two-CTA tcgen05 kernel covers head_dim 128 / 256 with tokens_per_page 16 / 32 and an even number of query heads per kv head", what);
+    set_error("%s: the two-CTA tcgen05 kernel covers head_dim 256, and head_dim 128 with an even number of query heads per kv head (tokens_per_page 16 / 32)", what);
     return PAL_ERR_UNSUPPORTED;
   }
   if (impl >= 2 && !tc_ok) {

@@ -22,18 +22,23 @@ int launch_prefill_tcgen05_pair_d128(const PrefillArgs& a, cudaStream_t stream);
 int launch_prefill_tcgen05_pair_d256(const PrefillArgs& a, cudaStream_t stream);
 
 bool prefill_tcgen05_pair_supports(int head_dim, int tokens_per_page, int num_q_heads, int num_kv_heads) {
-  return (head_dim == 128 || head_dim == 256) && (tokens_per_page == 16 || tokens_per_page == 32) && num_kv_heads > 0 &&
-         num_q_heads % num_kv_heads == 0 && (num_q_heads / num_kv_heads) % 2 == 0;
+  if (!(head_dim == 128 || head_dim == 256) || !(tokens_per_page == 16 || tokens_per_page == 32) || num_kv_heads <= 0 ||
+      num_q_heads % num_kv_heads != 0)
+    return false;
+  // head_dim 256 also pairs two query tiles of one head, which serves odd numbers of query heads per kv head
+  return head_dim == 256 || (num_q_heads / num_kv_heads) % 2 == 0;
 }
 
 int launch_prefill_tcgen05(const PrefillArgs& a, cudaStream_t stream) {
   const bool pair_ok = prefill_tcgen05_pair_supports(a.head_dim, a.tokens_per_page, a.num_q_heads, a.num_kv_heads);
   // impl 4 asks for the two-CTA form; head_dim 256 takes it by default (impl 3 keeps the one-CTA kernel)
   if (a.impl == 4 && !pair_ok) {
-    set_error("paged_attention_prefill: the two-CTA tcgen05 kernel covers head_dim 128 / 256 with tokens_per_page 16 / 32 and an even number of query heads per kv head");
+    set_error("paged_attention_prefill: the two-CTA tcgen05 kernel covers head_dim 256, and head_dim 128 with an even number of query heads per kv head (tokens_per_page 16 / 32)");
     return -2;
   }
-  if (pair_ok && (a.impl == 4 || (a.head_dim == 256 && a.impl != 3)))
+  // (odd groups with a single query tile per sequence gain nothing from pairing query tiles: the one-CTA kernel keeps them)
+  const bool odd_single_tile = (a.num_q_heads / a.num_kv_heads) % 2 != 0 && a.tokens_per_seq <= 128;
+  if (pair_ok && (a.impl == 4 || (a.head_dim == 256 && a.impl != 3 && !odd_single_tile)))
     return a.head_dim == 128 ? launch_prefill_tcgen05_pair_d128(a, stream) : launch_prefill_tcgen05_pair_d256(a, stream);
 #define PAL_TC_CALL(DD, TT) \
   if (a.head_dim == DD && a.tokens_per_page == TT) return launch_prefill_tcgen05_d##DD##_t##TT(a, stream);

@@ -1,10 +1,12 @@
 // Paged-attention prefill with tcgen05.mma.cta_group::2: two CTAs on the two SMs of a TPC work as one M = 256 MMA.
 //
 // Same operator as prefill_tcgen05.cuh (the reference's pal_paged_attention_prefill,
-// src/pal_core/kernels/paged_attention/prefill/paged_attention_prefill.h.metal:28-389), for head_dim 128 / 256 and an
-// even number of query heads per kv head.
+// src/pal_core/kernels/paged_attention/prefill/paged_attention_prefill.h.metal:28-389), for head_dim 256 and - with an
+// even number of query heads per kv head - head_dim 128.
 //
-// A cluster of two CTAs owns two query heads that share a kv head: CTA r holds the 128 rows of head h0 + r (Q in its
+// A cluster of two CTAs owns two accumulator tiles that read the same K / V tiles: 128 new tokens of two query heads that
+// share a kv head or, when the heads per kv head are odd in number (head_dim 256 only), two consecutive 128-token query
+// tiles of one head.  CTA r holds the 128 rows of tile r (Q in its
 // shared memory, S / P / O in its TMEM), and every MMA is issued once, by CTA 0, with M = 256.  The B operand of such an
 // MMA is split between the CTAs - each supplies half of the N rows from its own shared memory - so CTA r loads only
 // keys [64 r, 64 r + 64) of a K tile and head-dim columns [D/2 r, D/2 r + D/2) of a V tile.  Against one accumulator
@@ -131,7 +133,10 @@ __host__ __device__ constexpr uint32_t make_idesc_pair(int n, int a_fmt, int b_f
          ((uint32_t)(256 >> 4) << 24);
 }
 
-template <typename T, int D, int TPP>
+// PAIR_TILES = false: the pair's two accumulator tiles are one 128-token query tile of query heads 2k and 2k + 1 (which
+// share a kv head).  PAIR_TILES = true (odd numbers of query heads per kv head): they are query tiles 2t and 2t + 1 of one
+// head; both read every K / V tile up to the later tile's diagonal, and the earlier one sees its last key tile fully masked.
+template <typename T, int D, int TPP, bool PAIR_TILES>
 __global__ void __launch_bounds__(192, 1)
     prefill_tcgen05_pair_kernel(const TcParams p, const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_khalf,
                                 const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_vhalf,
@@ -160,9 +165,11 @@ __global__ void __launch_bounds__(192, 1)
   const uint32_t rank = cluster_ctarank();
   // Launch order (x fastest): the head pairs of a sequence's heaviest query tile, then its next query tile, ...;
   // sequences in order of decreasing work (see sequence_of_rank).  blockIdx.x = 2 * head pair + rank in the pair.
-  const int qt = (int)gridDim.y - 1 - (int)blockIdx.y;
+  const int qt_pair = (int)gridDim.y - 1 - (int)blockIdx.y;
+  const int qt = PAIR_TILES ? 2 * qt_pair + (int)rank : qt_pair;     // this CTA's query tile
   const int t0 = qt * kTile;
-  const int h = blockIdx.x;  // heads 2k and 2k + 1 form the pair and share a kv head
+  const int t0_first = PAIR_TILES ? 2 * qt_pair * kTile : t0;        // the pair's first query token
+  const int h = PAIR_TILES ? (int)(blockIdx.x >> 1) : (int)blockIdx.x;  // heads 2k and 2k + 1 form the pair, or one head does
   const int s = sequence_of_rank(p, blockIdx.z, lane, sequence_rank_key(p, lane));
   const int kvh = h / p.group;
   const bool ragged = p.cu_seqlens != nullptr;
@@ -170,7 +177,7 @@ __global__ void __launch_bounds__(192, 1)
   const int row0 = ragged ? p.cu_seqlens[s] : 0;
   const int tma_seq = ragged ? 0 : s;
   const size_t out_row0 = ragged ? (size_t)row0 : (size_t)s * N;
-  if (t0 >= N) return;  // both CTAs of a pair take the same branch; nothing is allocated yet
+  if (t0_first >= N) return;  // both CTAs of a pair take the same branch; nothing is allocated yet
   int H = p.hist_lens[s];
   if (H < 0 || p.num_pages <= 0) H = 0;
   {
@@ -178,9 +185,12 @@ __global__ void __launch_bounds__(192, 1)
     if (H > cap) H = (int)cap;
   }
   const int hist_tiles = (H + kTile - 1) / kTile;
-  const int num_tiles = hist_tiles + qt + 1;
+  // key tiles of the new tokens up to the diagonal of the pair's last query tile that exists
+  const int dense_tiles = PAIR_TILES ? (t0_first + kTile < N ? 2 * qt_pair + 2 : 2 * qt_pair + 1) : qt + 1;
+  const int num_tiles = hist_tiles + dense_tiles;
   // the rounding residual of P goes through a second set of PV MMAs where rows see few keys, or for float32 outputs
-  const bool split_p = Mma16816<T>::kSplitP && (p.out_f32 != 0 || H + t0 < 256);
+  // (decided for the pair as a whole: CTA 0 issues the MMAs of both)
+  const bool split_p = Mma16816<T>::kSplitP && (p.out_f32 != 0 || H + t0_first < 256);
   // Tiles whose V holds slots that must read as zero (0 * NaN would poison O): the last history tile when the history
   // ends inside it, and in ragged batches the dense tile that runs into the next sequence's rows.  Their V halves are
   // counted on the CTA's own v_local barrier (index 0 / 1), so that the CTA's softmax warps can wait for them.
@@ -535,7 +545,8 @@ __global__ void __launch_bounds__(192, 1)
         fence_proxy_async_smem();
         __syncwarp();
         if (lane == 0) mbar_arrive(e_bar);
-        if (lane_group == 0 && lane == 0 && mbar_wait(e_bar, 0, p.status)) {
+        // (with query tiles paired, the second one may lie entirely past the sequence's end: nothing to write then)
+        if (lane_group == 0 && lane == 0 && mbar_wait(e_bar, 0, p.status) && t0 < N) {
           for (int kb = 0; kb < kBlocks; ++kb) tma_store_4d(&tm_out, sQ + kb * kBlockBytes, kb * 64, h, row0 + t0, tma_seq);
           tma_store_commit_and_wait_read();
         }
@@ -616,11 +627,11 @@ const PairMaps* pair_maps_for(const PrefillArgs& a) {
   return &m;
 }
 
-template <typename T, int D, int TPP>
+template <typename T, int D, int TPP, bool PAIR_TILES>
 int launch_pair(const TcParams& p, const PairMaps& m, cudaStream_t stream) {
   using C = PairCfg<D, TPP>;
   static_assert(C::kTotal <= 227 * 1024, "prefill shared memory exceeds the per-CTA limit");
-  auto kern = prefill_tcgen05_pair_kernel<T, D, TPP>;
+  auto kern = prefill_tcgen05_pair_kernel<T, D, TPP, PAIR_TILES>;
   static DeviceOnce configured;
   const int rc = configured.run([&] { return (int)cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kTotal); });
   if (rc != 0) return rc;
@@ -632,7 +643,7 @@ int launch_pair(const TcParams& p, const PairMaps& m, cudaStream_t stream) {
   // (a cluster dimension given at compile time with a <<<>>> launch was rejected by the driver for the (1, 2, 1) shape;
   // the launch attribute with the pair along x is accepted)
   cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3(p.num_q_heads, num_qt, p.num_seqs);
+  cfg.gridDim = PAIR_TILES ? dim3(2 * p.num_q_heads, (num_qt + 1) / 2, p.num_seqs) : dim3(p.num_q_heads, num_qt, p.num_seqs);
   cfg.blockDim = dim3(192, 1, 1);
   cfg.dynamicSmemBytes = C::kTotal;
   cfg.stream = stream;
@@ -648,8 +659,8 @@ int launch_pair(const TcParams& p, const PairMaps& m, cudaStream_t stream) {
 
 template <int D, int TPP>
 int launch_pair_shape(const PrefillArgs& a, cudaStream_t stream) {
-  if (a.num_seqs > 65535 || a.num_q_heads > 65535) {
-    set_error("paged_attention_prefill: num_seqs and num_q_heads are limited to 65535");
+  if (a.num_seqs > 65535 || a.num_q_heads > 32767) {
+    set_error("paged_attention_prefill: num_seqs is limited to 65535 and num_q_heads to 32767");
     return -1;
   }
   if ((long long)a.num_pages * a.num_kv_heads * (D / 8) * (TPP / 16) > 0x7fffffffLL) {
@@ -674,7 +685,13 @@ int launch_pair_shape(const PrefillArgs& a, cudaStream_t stream) {
   p.scale_log2 = a.scale * kLog2e;
   const PairMaps* m = pair_maps_for<D, TPP>(a);
   if (!m) return -3;
-  return a.dtype == 0 ? launch_pair<__half, D, TPP>(p, *m, stream) : launch_pair<__nv_bfloat16, D, TPP>(p, *m, stream);
+  // heads that share a kv head pair up; with an odd number of heads per kv head two consecutive query tiles of one head do
+  if (p.group % 2 == 0)
+    return a.dtype == 0 ? launch_pair<__half, D, TPP, false>(p, *m, stream) : launch_pair<__nv_bfloat16, D, TPP, false>(p, *m, stream);
+  if constexpr (D == 256)
+    return a.dtype == 0 ? launch_pair<__half, D, TPP, true>(p, *m, stream) : launch_pair<__nv_bfloat16, D, TPP, true>(p, *m, stream);
+  set_error("paged_attention_prefill: the two-CTA tcgen05 kernel needs an even number of query heads per kv head at this head_dim");
+  return -2;
 }
 
 }  // namespace

@@ -113,6 +113,8 @@ def test_ragged_batches_on_the_two_cta_kernel(pal, cuda, d, tpp):
     counts = [1, 140, 0, 64, 129, 5, 128, 300]
     hist = [100, 0, 50, 129, 16, 300, 63, 1000]
     check(pal, cuda, make_ragged_case(31, hist, counts, 4, 2, d, tpp=tpp, poison_unused=True), "tcgen05_pair")
+    if d == 256:  # odd group: query tiles paired
+        check(pal, cuda, make_ragged_case(32, hist, counts, 3, 3, d, tpp=tpp, poison_unused=True), "tcgen05_pair")
 
 
 @pytest.mark.parametrize("impl", IMPLS)
