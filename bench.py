@@ -751,7 +751,7 @@ def measure(w, env, peaks, steps, warmup, blocks, e2e=True):
 # 0.904 x its algorithmic bytes (captured on the reduced case; the traffic grows with the tokens).
 PROFILED_TRAFFIC = {"decode_8b": 1.3866e9, "decode_8b_append": 1.3889e9}
 
-EXTRA_SINGLE = ["prefill_8b", "prefill_d256", "decode_70b", "decode_70b_auto", "fill", "fill_append"]
+EXTRA_SINGLE = ["prefill_8b", "prefill_ragged", "prefill_d256", "decode_8b_append", "decode_70b", "decode_70b_auto", "fill", "fill_append"]
 EXTRA_MULTI = ["decode_70b", "decode_70b_auto", "decode_70b_ctx", "decode_70b_ctx_fused", "decode_70b_ctx_fused_auto", "prefill_8b"]
 
 
