@@ -77,7 +77,46 @@ def build(force: bool = False, verbose: bool = False) -> Path:
         r = subprocess.run(cmd, capture_output=True, text=True)
         if r.returncode != 0:
             raise RuntimeError(f"link failed:\n{r.stdout}\n{r.stderr}")
+    build_fastpath(force=force)
     return LIB
+
+
+def fastpath_path() -> Path:
+    import sysconfig
+
+    return HERE / ("_pal_fast" + (sysconfig.get_config_var("EXT_SUFFIX") or ".so"))
+
+
+def build_fastpath(force: bool = False) -> Path:
+    """Compile csrc/torch_fastpath.cpp (the C++ front of the Python operators) against this interpreter's torch and link it
+    to libpal_b200.so; written next to the library.  Host code only: no GPU code lives in it."""
+    import sysconfig
+
+    import pybind11
+    import torch
+    from torch.utils import cpp_extension
+
+    src = CSRC / "torch_fastpath.cpp"
+    out = fastpath_path()
+    OBJ_DIR.mkdir(exist_ok=True)
+    stamp = OBJ_DIR / "torch_fastpath.stamp"
+    want = hashlib.sha256((_digest([src, HERE.parent / "include" / "pal_b200.h"]) + torch.__version__ + sys.version).encode()).hexdigest()
+    if not force and out.exists() and stamp.exists() and stamp.read_text() == want:
+        return out
+    cuda_home = os.environ.get("CUDA_HOME") or "/usr/local/cuda"
+    includes = [*cpp_extension.include_paths(), pybind11.get_include(), sysconfig.get_paths()["include"],
+                str(Path(cuda_home) / "include"), str(HERE.parent / "include")]
+    torch_lib = cpp_extension.library_paths()[0]
+    cmd = ["g++", "-O2", "-std=c++17", "-shared", "-fPIC", "-fvisibility=hidden", "-DTORCH_EXTENSION_NAME=_pal_fast",
+           "-DTORCH_API_INCLUDE_EXTENSION_H", f"-D_GLIBCXX_USE_CXX11_ABI={int(torch.compiled_with_cxx11_abi())}",
+           *[f"-I{i}" for i in includes], str(src), "-o", str(out),
+           f"-L{torch_lib}", "-ltorch", "-ltorch_cpu", "-ltorch_python", "-lc10", "-lc10_cuda",
+           f"-L{HERE}", "-l:libpal_b200.so", "-Wl,-rpath,$ORIGIN", f"-Wl,-rpath,{torch_lib}"]
+    r = subprocess.run(cmd, capture_output=True, text=True)
+    if r.returncode != 0:
+        raise RuntimeError(f"building the operator fast path failed:\n{r.stdout}\n{r.stderr}")
+    stamp.write_text(want)
+    return out
 
 
 if __name__ == "__main__":

@@ -21,6 +21,11 @@ import torch
 from . import _lib
 from ._lib import lib
 
+try:  # C++ front of the hot operators (csrc/torch_fastpath.cpp): same C-ABI calls, without ctypes and Python-side checks
+    from . import _pal_fast as _fast
+except ImportError:  # not built: every call takes the ctypes path below
+    _fast = None
+
 _DTYPES = {torch.float16: _lib.PAL_DTYPE_F16, torch.bfloat16: _lib.PAL_DTYPE_BF16}
 
 
@@ -200,6 +205,17 @@ def fill_kv_pages(
     """
     if slot_mapping is None and page_table is not None and current_token_write_positions is None and query_to_seq_map is None:
         slot_mapping, page_table = page_table, None
+    if _fast is not None and stream is None and inplace:
+        try:
+            if slot_mapping is not None:
+                done = page_table is None and _fast.fill(new_keys, new_values, global_key_pool, global_value_pool, slot_mapping, None, None)
+            else:
+                done = _fast.fill(new_keys, new_values, global_key_pool, global_value_pool, page_table, current_token_write_positions,
+                                  query_to_seq_map)
+        except TypeError:
+            done = False
+        if done:
+            return global_key_pool, global_value_pool
     for name, t in (("new_keys", new_keys), ("new_values", new_values), ("global_key_pool", global_key_pool),
                     ("global_value_pool", global_value_pool)):
         _need_cuda(name, t)
@@ -314,6 +330,17 @@ def paged_attention_decode(queries, k_cache_pool, v_cache_pool, page_table, sequ
     ``partition_pages``: None = let the library choose, 0 = fused single pass, n > 0 = two-pass split-KV with n-page
     partitions and a log-sum-exp combine.
     """
+    if _fast is not None and stream is None and (out_dtype is None or out_dtype is torch.float32):
+        # the common case (3-D queries, contiguous tensors, 32-bit indices, a workspace from an earlier call) from C++;
+        # None means "not the common case": the checks and conversions below then run as usual
+        try:
+            out = _fast.decode(queries, k_cache_pool, v_cache_pool, page_table, sequence_lengths,
+                               _lib.PAL_DECODE_AUTO if partition_pages is None else int(partition_pages),
+                               0.0 if scale is None else float(scale), out_dtype is torch.float32, _WORKSPACES, None, None)
+        except TypeError:
+            out = None
+        if out is not None:
+            return out
     S, hq, hkv, d, tpp, num_pages = _decode_shapes(queries, k_cache_pool, v_cache_pool, page_table, sequence_lengths)
     dev = queries.device
     code, odt = _out_code(queries.dtype, out_dtype)
@@ -344,6 +371,15 @@ def paged_attention_decode_append(new_keys, new_values, queries, k_cache_pool, v
     count the new token).  The pools are updated in place exactly as ``fill_kv_pages`` would; returns the
     attention output ``[S, Hq, D]``.
     """
+    if _fast is not None and stream is None and (out_dtype is None or out_dtype is torch.float32):
+        try:
+            out = _fast.decode(queries, k_cache_pool, v_cache_pool, page_table, sequence_lengths,
+                               _lib.PAL_DECODE_AUTO if partition_pages is None else int(partition_pages),
+                               0.0 if scale is None else float(scale), out_dtype is torch.float32, _WORKSPACES, new_keys, new_values)
+        except TypeError:
+            out = None
+        if out is not None:
+            return out
     S, hq, hkv, d, tpp, num_pages = _decode_shapes(queries, k_cache_pool, v_cache_pool, page_table, sequence_lengths)
     for name, t in (("new_keys", new_keys), ("new_values", new_values)):
         _need_cuda(name, t)
@@ -493,6 +529,15 @@ def paged_attention_prefill(q_prompt, k_prompt, v_prompt, k_cache_paged, v_cache
     (``src/pal_core/src/paged_attention_prefill_primitive.cpp:188-192``), in the query dtype or, with
     ``out_dtype=torch.float32``, in float32.
     """
+    if _fast is not None and stream is None and (out_dtype is None or out_dtype is torch.float32) and (impl in PREFILL_IMPL or type(impl) is int):
+        try:
+            out = _fast.prefill(q_prompt, k_prompt, v_prompt, k_cache_paged, v_cache_paged, page_table, context_len_arr,
+                                PREFILL_IMPL[impl] if type(impl) is str else impl, 0.0 if scale is None else float(scale),
+                                out_dtype is torch.float32, _WORKSPACES)
+        except TypeError:
+            out = None
+        if out is not None:
+            return out
     S, total, hq, hkv, d, tpp, num_pages = _prefill_shapes(q_prompt, k_prompt, v_prompt, k_cache_paged, v_cache_paged,
                                                            page_table, context_len_arr)
     if S == 0 or total % S != 0:

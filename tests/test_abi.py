@@ -182,3 +182,19 @@ def test_prefill_impl_argument_is_validated_before_anything_runs():
     assert call(4, 2, 64, 4) == _lib.PAL_ERR_UNSUPPORTED and "two-CTA" in _lib.last_error()
     assert call(3, 3, 128, 4) == _lib.PAL_ERR_UNSUPPORTED
     assert call(4, 2, 48, 2) == _lib.PAL_ERR_UNSUPPORTED
+
+
+def test_cpp_front_is_built_and_declines_what_it_does_not_handle():
+    """The operators' C++ front end (csrc/torch_fastpath.cpp) loads beside the library, and answers None / False for calls
+    that are not its common case - here CPU tensors - so that the Python path behind it raises the usual errors."""
+    import torch
+
+    from proxy_attention_lab_b200 import ops
+
+    assert ops._fast is not None
+    x = torch.zeros((2, 4, 64), dtype=torch.float16)
+    assert ops._fast.decode(x, x, x, x, x, 0, 0.0, False, {}, None, None) is None
+    assert ops._fast.prefill(x, x, x, x, x, x, x, 0, 0.0, False, {}) is None
+    assert ops._fast.fill(x, x, x, x, x, None, None) is False
+    with pytest.raises(RuntimeError):
+        ops.paged_attention_decode(x, x, x, x, x)

@@ -131,3 +131,48 @@ def test_out_dtype_is_checked(pal, cuda):
         pal.paged_attention_decode(t["q"], t["k_pool"], t["v_pool"], t["page_table"], t["lens"], out_dtype=torch.bfloat16)
     out = pal.paged_attention_decode(t["q"], t["k_pool"], t["v_pool"], t["page_table"], t["lens"], out_dtype=torch.float16)
     assert out.dtype == torch.float16
+
+
+def test_cpp_front_and_ctypes_path_agree(pal, cuda, monkeypatch):
+    """The operators' C++ front (the common case) and the ctypes path behind it make the same C-ABI calls: identical
+    outputs for decode, append + decode, prefill and fill; and what the front declines (int64 page table, 2-D queries,
+    a side stream) still works."""
+    from proxy_attention_lab_b200 import ops
+
+    assert ops._fast is not None, "the C++ front was not built (proxy_attention_lab_b200/build.py builds it)"
+    g = torch.Generator(device=cuda).manual_seed(3)
+    S, hq, hkv, d, tpp, P = 3, 8, 2, 128, 16, 24
+    mk = lambda *shape: torch.randn(shape, device=cuda, dtype=torch.bfloat16, generator=g)
+    q, kp, vp = mk(S, hq, d), mk(P, hkv, d // 8, tpp, 8), mk(P, hkv, d, tpp)
+    table = torch.randperm(P, device=cuda).reshape(S, P // S).to(torch.int32)
+    lens = torch.tensor([100, 17, 128], dtype=torch.int32, device=cuda)
+    qp, kn, vn = mk(S * 70, hq, d), mk(S * 70, hkv, d), mk(S * 70, hkv, d)
+    nk, nv = mk(S, hkv, d), mk(S, hkv, d)
+    slots = torch.tensor([5, 77, 300], dtype=torch.int64, device=cuda)
+
+    def run_all():
+        k2, v2 = kp.clone(), vp.clone()
+        outs = [pal.paged_attention_decode(q, kp, vp, table, lens), pal.paged_attention_decode(q, kp, vp, table, lens, partition_pages=2),
+                pal.paged_attention_decode(q, kp, vp, table, lens, out_dtype=torch.float32),
+                pal.paged_attention_prefill(qp, kn, vn, kp, vp, table, lens),
+                pal.paged_attention_decode_append(nk, nv, q, k2, v2, table, lens)]
+        pal.fill_kv_pages(nk, nv, k2, v2, slots)
+        pal.fill_kv_pages(nk, nv, k2, v2, table, lens - 1, torch.arange(S, dtype=torch.int32, device=cuda))
+        torch.cuda.synchronize()
+        return [o.cpu() for o in outs] + [k2.cpu(), v2.cpu()]
+
+    fast = run_all()
+    monkeypatch.setattr(ops, "_fast", None)
+    slow = run_all()
+    for a, b in zip(fast, slow):
+        assert a.dtype == b.dtype and torch.equal(a.view(torch.int16) if a.dtype != torch.float32 else a, b.view(torch.int16) if b.dtype != torch.float32 else b)
+    monkeypatch.undo()
+    # declined by the front, served by the path behind it
+    ref = pal.paged_attention_decode(q, kp, vp, table, lens).cpu()
+    assert torch.equal(pal.paged_attention_decode(q, kp, vp, table.to(torch.int64), lens).cpu().view(torch.int16), ref.view(torch.int16))
+    side = torch.cuda.Stream(device=cuda)
+    side.wait_stream(torch.cuda.current_stream(cuda))
+    out_side = pal.paged_attention_decode(q, kp, vp, table, lens, stream=side)
+    side.synchronize()
+    assert torch.equal(out_side.cpu().view(torch.int16), ref.view(torch.int16))
+    pal.check_status()
