@@ -250,8 +250,10 @@ int pal_paged_attention_decode_ctx_exchange(const void* queries, const void* k_p
                                             int world_size, int rank, int64_t rows_capacity, void* stream);
 
 /* ---- paged_attention_prefill -------------------------------------------------------------- */
-/* The prefill kernels need the 256-byte workspace header only: this returns 256 for every problem (the
- * arguments are there so that the answer can depend on them later without an ABI change). */
+/* Bytes of workspace a prefill call of this shape can use (tokens_per_seq: the uniform count, or the longest sequence's
+ * count for the ragged form): the 256-byte header, plus - for batches too small to give every SM a CTA - room for the
+ * fp32 partial results of a launch that is cut along the history (at most 32 MB).  A call given only the header still
+ * works; it runs uncut. */
 size_t pal_prefill_workspace_bytes(int num_seqs, int tokens_per_seq, int num_q_heads,
                                    int num_kv_heads, int head_dim);
 

@@ -491,12 +491,7 @@ int pal_lse_combine_packed(const float* packed, void* out, int num_parts, int64_
 // status word, whatever the problem size (the arguments exist so that a later kernel may need more without an ABI change).
 size_t pal_prefill_workspace_bytes(int num_seqs, int tokens_per_seq, int num_q_heads, int num_kv_heads,
                                    int head_dim) {
-  (void)num_seqs;
-  (void)tokens_per_seq;
-  (void)num_q_heads;
-  (void)num_kv_heads;
-  (void)head_dim;
-  return sizeof(WorkspaceHeader);
+  return prefill_workspace_bytes(num_seqs, tokens_per_seq, num_q_heads, num_kv_heads, head_dim);
 }
 
 // tokens_per_seq is the uniform count, or with cu_seqlens (ragged form) the longest sequence's count

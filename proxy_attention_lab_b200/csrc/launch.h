@@ -159,6 +159,10 @@ int launch_exchange_combine(const ExchangeArgs& a, cudaStream_t stream);
 int launch_prefill_mma(const PrefillArgs& a, cudaStream_t stream);
 int launch_prefill_tcgen05(const PrefillArgs& a, cudaStream_t stream);
 bool prefill_tcgen05_supports(int head_dim, int tokens_per_page);
+// Parts into which the tcgen05 prefill kernel would cut the history of this batch (1 = not at all), and the workspace
+// that takes: a function of the shape alone, so that the size can be asked for before the page table exists.
+int prefill_split_parts(int num_seqs, int tokens_per_seq, int num_q_heads, int num_kv_heads, int head_dim);
+size_t prefill_workspace_bytes(int num_seqs, int tokens_per_seq, int num_q_heads, int num_kv_heads, int head_dim);
 bool prefill_tcgen05_pair_supports(int head_dim, int tokens_per_page, int num_q_heads, int num_kv_heads);
 
 size_t decode_workspace_bytes(int num_seqs, int num_q_heads, int num_kv_heads, int head_dim, int tokens_per_page,

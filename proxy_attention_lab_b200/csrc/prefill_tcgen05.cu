@@ -1,5 +1,6 @@
 // Dispatch of the tcgen05 prefill kernel over its instantiations (head_dim 32 / 64 / 80 / 96 / 128 / 256 x tokens_per_page 16 / 32);
 // the kernel itself is in prefill_tcgen05.cuh, one translation unit per shape.
+#include "common.cuh"
 #include "launch.h"
 
 namespace pal {
@@ -15,6 +16,31 @@ bool prefill_tcgen05_supports(int head_dim, int tokens_per_page) {
   PAL_TC_SHAPES(PAL_TC_TEST)
 #undef PAL_TC_TEST
   return false;
+}
+
+int prefill_split_parts(int num_seqs, int tokens_per_seq, int num_q_heads, int num_kv_heads, int head_dim) {
+  if (head_dim == 256 || num_seqs <= 0 || tokens_per_seq <= 0 || num_q_heads <= 0 || num_kv_heads <= 0) return 1;  // 256: the two-CTA kernel
+  const long long qt = (tokens_per_seq + 127) / 128;
+  const int group = num_q_heads / num_kv_heads;
+  // CTAs of the unsplit launch: two heads of a kv head per CTA, or (odd groups) two query tiles of one head, or one tile
+  const long long ctas = group % 2 == 0 ? (long long)num_seqs * qt * (num_q_heads / 2)
+                                        : (tokens_per_seq > 128 ? (long long)num_seqs * ((qt + 1) / 2) * num_q_heads : (long long)num_seqs * num_q_heads);
+  // Cutting pays while all parts still run at once: every CTA carries ~9 us of fixed cost, so a second wave of smaller
+  // CTAs is slower than one wave of whole ones (measured: 8 sequences x 16 tokens over 2048, 128 CTAs: 45 us whole, 68 us in
+  // three parts).
+  constexpr long long kSms = 148;
+  if (2 * ctas > kSms) return 1;
+  long long parts = kSms / ctas;
+  if (parts > 16) parts = 16;
+  const long long rows = (long long)num_seqs * tokens_per_seq * num_q_heads;
+  while (parts > 1 && rows * parts * (head_dim + 2) * 4 > (32ll << 20)) --parts;  // partial triples: at most 32 MB
+  return parts < 2 ? 1 : (int)parts;
+}
+
+size_t prefill_workspace_bytes(int num_seqs, int tokens_per_seq, int num_q_heads, int num_kv_heads, int head_dim) {
+  const int parts = prefill_split_parts(num_seqs, tokens_per_seq, num_q_heads, num_kv_heads, head_dim);
+  if (parts < 2) return sizeof(WorkspaceHeader);
+  return sizeof(WorkspaceHeader) + (size_t)num_seqs * tokens_per_seq * num_q_heads * parts * (head_dim + 2) * sizeof(float);
 }
 
 // The two-CTA form (prefill_tcgen05_pair.cuh): head_dim 128 / 256, an even number of query heads per kv head.

@@ -111,6 +111,13 @@ struct TcParams {
   int num_seqs, n_new, num_q_heads, num_kv_heads, group, max_pages_per_seq;
   long long num_pages;
   float scale_log2;
+  // History split across CTAs (parts > 1): blockIdx.z counts (sequence, part); part k attends to history tiles
+  // [k * split_tiles, (k + 1) * split_tiles), the last part also to the new tokens; every CTA writes the un-normalised
+  // fp32 triple of its rows - acc [row][part][D], m (natural-log units) and l [row][part] - and a combine kernel merges them.
+  int parts, split_tiles;
+  float* part_acc;
+  float* part_m;
+  float* part_l;
 };
 
 // ---- PTX wrappers ---------------------------------------------------------------------------
@@ -431,7 +438,8 @@ __global__ void __launch_bounds__(64 + 128 * NQ, 1)
     if (t0 >= p.n_new) return;
     set_up();
   }
-  const int s = sequence_of_rank(p, blockIdx.z, lane, rank_key);
+  const int part = p.parts > 1 ? (int)(blockIdx.z % (unsigned)p.parts) : 0;
+  const int s = sequence_of_rank(p, p.parts > 1 ? (int)(blockIdx.z / (unsigned)p.parts) : (int)blockIdx.z, lane, rank_key);
   const int kvh = h0 / p.group;
   // Uniform batches index the prompt tensors as [sequence][token] (rows past N read as zero); ragged batches as one
   // flat row axis starting at the sequence's first row (rows past N belong to the next sequence and are masked).
@@ -457,10 +465,20 @@ __global__ void __launch_bounds__(64 + 128 * NQ, 1)
     const long long cap = (long long)p.max_pages_per_seq * TPP;
     if (H > cap) H = (int)cap;
   }
+  const int H_total = H;
+  int page0 = 0;           // first page of the history this CTA reads
+  bool with_new = true;    // ... and whether it also attends to the new tokens
+  if (p.parts > 1) {
+    const int first = part * p.split_tiles * kTile;
+    const int last = min(H_total, first + p.split_tiles * kTile);
+    H = last > first ? last - first : 0;
+    page0 = first / TPP;
+    with_new = part == p.parts - 1;
+  }
   const int hist_tiles = (H + kTile - 1) / kTile;
   // key tiles of the new tokens up to the diagonal of the CTA's last query tile that exists
-  const int dense_tiles = (PAIR_TILES && t0 + kTile < N ? qt + 1 : qt) + 1;
-  const int num_tiles = hist_tiles + dense_tiles;
+  const int dense_tiles = with_new ? (PAIR_TILES && t0 + kTile < N ? qt + 1 : qt) + 1 : 0;
+  const int num_tiles = hist_tiles + dense_tiles;  // (0 for a part that lies past the end of a short history)
   // bf16 rounds P with a relative error of up to 2^-8; summed over n keys that leaves about
   // 0.002 / sqrt(n / 3) of absolute error per unit of |v|, which only drops below the 2e-3 target
   // (at the 6-sigma level) once a row sees a few hundred keys.  CTAs that hold rows with fewer than
@@ -469,7 +487,7 @@ __global__ void __launch_bounds__(64 + 128 * NQ, 1)
   // PV MMAs.
   // A caller that asks for a float32 output asks for the arithmetic error alone to stay within tolerance on every row,
   // including rows dominated by a single key, where the rounding of P shows undiluted: the residual is then always fed.
-  const bool split_p = Mma16816<T>::kSplitP && (p.out_f32 != 0 || H + t0 < 256);
+  const bool split_p = Mma16816<T>::kSplitP && (p.out_f32 != 0 || H_total + t0 < 256);
 
   tc_fence_before();
   __syncthreads();
@@ -492,7 +510,7 @@ __global__ void __launch_bounds__(64 + 128 * NQ, 1)
       if (paged) {
         npg = min(kPagesPerTile, (H - j * kTile + TPP - 1) / TPP);
         if (lane < npg) {
-          my_pid = p.page_table[(size_t)s * p.max_pages_per_seq + j * kPagesPerTile + lane];
+          my_pid = p.page_table[(size_t)s * p.max_pages_per_seq + page0 + j * kPagesPerTile + lane];
           if ((long long)my_pid >= p.num_pages) my_pid = (uint32_t)(p.num_pages - 1);
         }
       }
@@ -629,6 +647,7 @@ __global__ void __launch_bounds__(64 + 128 * NQ, 1)
         tc_commit(&o_done[SBUF == 2 ? (j & 1) : q]);  // one accumulator tile: the two barriers alternate by key tile
       };
 
+      if (num_tiles == 0) ok = false;  // a part past the end of a short history: Q has landed, there is nothing to multiply
       if (ok) ok = wait_all(&k_full[0], 0);
       if (ok) {
         tc_fence_after();
@@ -786,7 +805,36 @@ __global__ void __launch_bounds__(64 + 128 * NQ, 1)
     }
 
     // ---- epilogue: O / l -> out[((s*N + qi)*Hq + h0 + q)*D + d] ----
-    if (ok) ok = wait_pv_done(num_tiles - 1);
+    if (ok && num_tiles > 0) ok = wait_pv_done(num_tiles - 1);
+    if (p.parts > 1) {
+      // this CTA's share of the keys: the un-normalised triple of every row goes to the partial buffers
+      // (the TMEM loads are warp-wide instructions: every lane takes part, only the stores depend on the row)
+      if (ok) {
+        tc_fence_after();
+        const size_t prow = ((out_row0 + qi) * p.num_q_heads + h0 + q * kHeadStep) * (size_t)p.parts + part;
+        const bool any = num_tiles > 0 && m_used > -INFINITY;
+        if (qi < N) {
+          p.part_m[prow] = any ? m_used * kLn2 : -INFINITY;
+          p.part_l[prow] = any ? l_run : 0.f;
+        }
+        if (num_tiles > 0) {
+          float4* pacc = reinterpret_cast<float4*>(p.part_acc + prow * D);
+#pragma unroll
+          for (int c4 = 0; c4 < D / kOC; ++c4) {
+            uint32_t v[kOC];
+            tmem_ldw(tO + c4 * kOC, v);
+            tmem_wait_ld();
+            if (qi < N && any) {
+#pragma unroll
+              for (int i = 0; i < kOC / 4; ++i)
+                pacc[c4 * (kOC / 4) + i] = make_float4(__uint_as_float(v[4 * i]), __uint_as_float(v[4 * i + 1]), __uint_as_float(v[4 * i + 2]),
+                                                       __uint_as_float(v[4 * i + 3]));
+            }
+          }
+        }
+      }
+      ok = false;  // nothing else to store
+    }
     // Full tiles (and partial ones of uniform batches, which the tensor map clips at the sequence's end) leave through
     // shared memory: the tile's Q buffer is no longer read by any MMA, has exactly the size and swizzled layout of the
     // output tile, and TMA stores write it out in whole lines.  A partial tile of a ragged batch would run into the
@@ -967,7 +1015,7 @@ int launch_tc(const TcParams& p, const TcMaps& m, cudaStream_t stream) {
   const int rc = configured.run([&] { return (int)cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kTotal); });
   if (rc != 0) return rc;
   const int num_qt = (p.n_new + kTile - 1) / kTile;
-  dim3 grid(PAIR_TILES ? p.num_q_heads : p.num_q_heads / NQ, PAIR_TILES ? (num_qt + 1) / 2 : num_qt, p.num_seqs);
+  dim3 grid(PAIR_TILES ? p.num_q_heads : p.num_q_heads / NQ, PAIR_TILES ? (num_qt + 1) / 2 : num_qt, p.num_seqs * p.parts);
   if (grid.y > 65535) {
     set_error("paged_attention_prefill: more than 65535 query tiles per sequence");
     return -2;
@@ -1017,9 +1065,35 @@ int launch_tc_shape(const PrefillArgs& a, cudaStream_t stream) {
   p.max_pages_per_seq = a.max_pages_per_seq;
   p.num_pages = a.num_pages;
   p.scale_log2 = a.scale * kLog2e;
+  // A batch that gives the GPU less than one CTA per SM has every CTA walk its sequence's whole history alone.  Such a
+  // batch is cut along the history instead (as the decode kernel's split pass does): parts x as many CTAs, each with
+  // 1 / parts of the history tiles, fp32 partial triples in the caller's workspace, one combine launch.  The workspace
+  // size the caller was told (pal_prefill_workspace_bytes) plans for it; a smaller workspace simply runs unsplit.
+  p.parts = 1;
+  p.split_tiles = 0;
+  p.part_acc = p.part_m = p.part_l = nullptr;
+  const long long rows = (a.cu_seqlens ? a.total_tokens : (long long)a.num_seqs * a.tokens_per_seq) * a.num_q_heads;
+  const int planned = prefill_split_parts(a.num_seqs, a.tokens_per_seq, a.num_q_heads, a.num_kv_heads, D);
+  const int hist_tiles_max = (int)(((long long)a.max_pages_per_seq * TPP + kTile - 1) / kTile);
+  if (planned > 1 && hist_tiles_max >= 2 && a.num_pages > 0 && rows > 0) {
+    int split_tiles = (hist_tiles_max + planned - 1) / planned;
+    if (split_tiles < 2) split_tiles = 2;  // a CTA's fixed cost is worth several key tiles
+    const int parts = (hist_tiles_max + split_tiles - 1) / split_tiles;
+    const size_t need = sizeof(WorkspaceHeader) + (size_t)rows * parts * (D + 2) * sizeof(float);
+    if (parts >= 2 && a.workspace_bytes >= need && (long long)a.num_seqs * parts <= 65535) {
+      p.parts = parts;
+      p.split_tiles = split_tiles;
+      p.part_acc = reinterpret_cast<float*>(static_cast<unsigned char*>(a.workspace) + sizeof(WorkspaceHeader));
+      p.part_m = p.part_acc + (size_t)rows * parts * D;
+      p.part_l = p.part_m + (size_t)rows * parts;
+    }
+  }
   const TcMaps* m = tensor_maps_for<D, TPP>(a);
   if (!m) return -3;
-  return a.dtype == 0 ? launch_tc_dtype<__half, D, TPP>(a, p, *m, stream) : launch_tc_dtype<__nv_bfloat16, D, TPP>(a, p, *m, stream);
+  const int rc = a.dtype == 0 ? launch_tc_dtype<__half, D, TPP>(a, p, *m, stream) : launch_tc_dtype<__nv_bfloat16, D, TPP>(a, p, *m, stream);
+  if (rc != 0 || p.parts == 1) return rc;
+  const PartialsView in{p.part_m, p.part_l, p.part_acc, 1, p.parts, D, (long long)p.parts * D};
+  return launch_lse_combine(in, a.out, a.out_f32, TripleOut{}, p.parts, rows, D, a.dtype, stream);
 }
 
 }  // namespace

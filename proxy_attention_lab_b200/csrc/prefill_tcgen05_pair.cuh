@@ -683,6 +683,9 @@ int launch_pair_shape(const PrefillArgs& a, cudaStream_t stream) {
   p.max_pages_per_seq = a.max_pages_per_seq;
   p.num_pages = a.num_pages;
   p.scale_log2 = a.scale * kLog2e;
+  p.parts = 1;  // (the history split of the one-CTA kernel is not used here)
+  p.split_tiles = 0;
+  p.part_acc = p.part_m = p.part_l = nullptr;
   const PairMaps* m = pair_maps_for<D, TPP>(a);
   if (!m) return -3;
   // heads that share a kv head pair up; with an odd number of heads per kv head two consecutive query tiles of one head do

@@ -116,7 +116,8 @@ py::object prefill(const at::Tensor& q, const at::Tensor& k, const at::Tensor& v
   c10::cuda::CUDAGuard guard(dev);
   const cudaStream_t stream = c10::cuda::getCurrentCUDAStream(dev.index()).stream();
   size_t ws_bytes = 0;
-  void* ws = held_workspace(registry, dev.index(), stream, 256, &ws_bytes);
+  const size_t need = pal_prefill_workspace_bytes((int)S, (int)(total / S), (int)hq, (int)hkv, (int)d);
+  void* ws = held_workspace(registry, dev.index(), stream, need > 256 ? need : 256, &ws_bytes);
   if (!ws) return py::none();
   at::Tensor out = at::empty({total * hq, d}, q.options().dtype(out_f32 ? at::kFloat : q.scalar_type()));
   const int rc = pal_paged_attention_prefill(q.data_ptr(), k.data_ptr(), v.data_ptr(), k_pool.data_ptr(), v_pool.data_ptr(),

@@ -130,6 +130,11 @@ def _decode_ws_bytes(S, hq, hkv, d, tpp, mp, pp) -> int:
     return lib.pal_decode_workspace_bytes(S, hq, hkv, d, tpp, mp, pp)
 
 
+@functools.lru_cache(maxsize=256)
+def _prefill_ws_bytes(S, n, hq, hkv, d) -> int:
+    return lib.pal_prefill_workspace_bytes(S, n, hq, hkv, d)
+
+
 def resolve_partition_pages(partition_pages, S, hq, hkv, d, tpp, max_pages) -> int:
     """Partition size of a split-KV pass that always splits (the partials forms): a positive request is taken as it is,
     ``None`` / ``PAL_DECODE_AUTO`` asks the library, and where the library would run a single pass the whole page table
@@ -553,7 +558,7 @@ def paged_attention_prefill(q_prompt, k_prompt, v_prompt, k_cache_paged, v_cache
         q, k, v = _contig(q_prompt), _contig(k_prompt), _contig(v_prompt)
         pt = _index32("page_table", page_table)
         ctx = _index32("context_len_arr", context_len_arr)
-        ws = _workspace(256, dev, sp)
+        ws = _workspace(_prefill_ws_bytes(S, n, hq, hkv, d), dev, sp)
         rc = lib.pal_paged_attention_prefill(q.data_ptr(), k.data_ptr(), v.data_ptr(), _ptr(k_cache_paged), _ptr(v_cache_paged),
                                              _ptr(pt), ctx.data_ptr(), out.data_ptr(), S, n, hq, hkv, d, tpp, num_pages,
                                              pt.shape[1], 0.0 if scale is None else float(scale), code,
@@ -589,7 +594,7 @@ def paged_attention_prefill_ragged(q_prompt, k_prompt, v_prompt, k_cache_paged, 
         q, k, v = _contig(q_prompt), _contig(k_prompt), _contig(v_prompt)
         pt = _index32("page_table", page_table)
         ctx = _index32("context_len_arr", context_len_arr)
-        ws = _workspace(256, dev, sp)
+        ws = _workspace(_prefill_ws_bytes(S, int(max_new_tokens), hq, hkv, d), dev, sp)
         rc = lib.pal_paged_attention_prefill_ragged(q.data_ptr(), k.data_ptr(), v.data_ptr(), _ptr(k_cache_paged),
                                                     _ptr(v_cache_paged), _ptr(pt), ctx.data_ptr(), cu.data_ptr(), out.data_ptr(),
                                                     S, total, int(max_new_tokens), hq, hkv, d, tpp, num_pages, pt.shape[1],

@@ -230,3 +230,20 @@ def test_two_cta_kernel_equals_the_one_cta_kernel_bit_for_bit(pal, cuda, d, dtyp
     single = run_prefill(pal, case, cuda, impl="tcgen05_single")
     assert torch.equal(pair, single)
     pal.check_status()
+
+
+@pytest.mark.parametrize("impl", ["tcgen05", "tcgen05_single"])
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("d,tpp", [(128, 16), (64, 32), (96, 16), (32, 16)])
+def test_small_batches_are_cut_along_the_history(pal, cuda, impl, dtype, d, tpp):
+    """A batch that gives the GPU less than one CTA per SM is cut along the history (parts of the history tiles per CTA, fp32
+    partial triples, one combine launch): one token over a long history, a few tokens over histories of very different
+    lengths (the short one leaves most parts empty), more than one query tile, even and odd groups, no history at all."""
+    for hq, hkv, hist, n in ((8, 2, [4096], 1), (4, 2, [3000, 50], 16), (3, 3, [1000], 130), (8, 2, [0, 0], 5), (2, 1, [129, 2047, 128], 64)):
+        case = make_prefill_case(90 + d + n, hist, n, hq, hkv, d, tpp=tpp, dtype=dtype, poison_unused=True)
+        check(pal, cuda, case, impl)
+    from proxy_attention_lab_b200._lib import lib
+
+    assert lib.pal_prefill_workspace_bytes(1, 1, 8, 2, d) > 256
+    assert lib.pal_prefill_workspace_bytes(8, 2048, 32, 8, d) == 256
+    pal.check_status()

@@ -117,6 +117,15 @@ def test_ragged_batches_on_the_two_cta_kernel(pal, cuda, d, tpp):
         check(pal, cuda, make_ragged_case(32, hist, counts, 3, 3, d, tpp=tpp, poison_unused=True), "tcgen05_pair")
 
 
+@pytest.mark.parametrize("impl", ["tcgen05", "tcgen05_single"])
+@pytest.mark.parametrize("d", [128, 64])
+def test_small_ragged_batches_are_cut_along_the_history(pal, cuda, impl, d):
+    """Decode steps and short chunks in one ragged call, too few CTAs to fill the GPU: the launch is cut along the history."""
+    counts = [1, 20, 5, 0, 1]
+    hist = [2000, 0, 700, 300, 4000]
+    check(pal, cuda, make_ragged_case(41, hist, counts, 8, 2, d, poison_unused=True), impl)
+
+
 @pytest.mark.parametrize("impl", IMPLS)
 def test_equal_counts_match_the_uniform_call_bit_for_bit(pal, cuda, impl):
     counts = [192] * 3
