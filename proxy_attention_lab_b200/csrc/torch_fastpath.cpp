@@ -95,9 +95,10 @@ py::object decode(const at::Tensor& q, const at::Tensor& k_pool, const at::Tenso
   return py::cast(out);
 }
 
-// paged_attention_prefill (uniform batches)
+// paged_attention_prefill (uniform batches) / paged_attention_prefill_ragged (cu_seqlens and the longest count given)
 py::object prefill(const at::Tensor& q, const at::Tensor& k, const at::Tensor& v, const at::Tensor& k_pool, const at::Tensor& v_pool,
-                   const at::Tensor& page_table, const at::Tensor& hist, int impl, double scale, bool out_f32, const py::dict& registry) {
+                   const at::Tensor& page_table, const at::Tensor& hist, int impl, double scale, bool out_f32, const py::dict& registry,
+                   const c10::optional<at::Tensor>& cu_seqlens, int max_new_tokens) {
   if (!q.is_cuda()) return py::none();
   const c10::Device dev = q.device();
   const int code = dtype_code(q);
@@ -108,7 +109,11 @@ py::object prefill(const at::Tensor& q, const at::Tensor& k, const at::Tensor& v
   if (!dense_cuda(page_table, dev) || !dense_cuda(hist, dev) || !int32_like(page_table) || !int32_like(hist)) return py::none();
   const int64_t num_pages = v_pool.size(0), hkv = v_pool.size(1), d = v_pool.size(2), tpp = v_pool.size(3);
   const int64_t S = page_table.size(0), mp = page_table.size(1), total = q.size(0), hq = q.size(1);
-  if (S == 0 || total == 0 || total % S != 0 || num_pages == 0 || mp == 0 || hkv == 0 || hq % hkv != 0 || q.size(2) != d ||
+  const bool ragged = cu_seqlens.has_value();
+  if (ragged && (!dense_cuda(*cu_seqlens, dev) || !int32_like(*cu_seqlens) || cu_seqlens->dim() != 1 || cu_seqlens->numel() != S + 1 ||
+                 max_new_tokens <= 0))
+    return py::none();
+  if (S == 0 || total == 0 || (!ragged && total % S != 0) || num_pages == 0 || mp == 0 || hkv == 0 || hq % hkv != 0 || q.size(2) != d ||
       k.size(0) != total || v.size(0) != total || k.size(1) != hkv || v.size(1) != hkv || k.size(2) != d || v.size(2) != d ||
       hist.numel() < S || k_pool.size(0) != num_pages || k_pool.size(1) != hkv || k_pool.size(2) * 8 != d || k_pool.size(3) != tpp ||
       k_pool.size(4) != 8)
@@ -116,14 +121,22 @@ py::object prefill(const at::Tensor& q, const at::Tensor& k, const at::Tensor& v
   c10::cuda::CUDAGuard guard(dev);
   const cudaStream_t stream = c10::cuda::getCurrentCUDAStream(dev.index()).stream();
   size_t ws_bytes = 0;
-  const size_t need = pal_prefill_workspace_bytes((int)S, (int)(total / S), (int)hq, (int)hkv, (int)d);
+  const int per_seq = ragged ? max_new_tokens : (int)(total / S);
+  const size_t need = pal_prefill_workspace_bytes((int)S, per_seq, (int)hq, (int)hkv, (int)d);
   void* ws = held_workspace(registry, dev.index(), stream, need > 256 ? need : 256, &ws_bytes);
   if (!ws) return py::none();
   at::Tensor out = at::empty({total * hq, d}, q.options().dtype(out_f32 ? at::kFloat : q.scalar_type()));
-  const int rc = pal_paged_attention_prefill(q.data_ptr(), k.data_ptr(), v.data_ptr(), k_pool.data_ptr(), v_pool.data_ptr(),
-                                             page_table.data_ptr(), static_cast<const int32_t*>(hist.data_ptr()), out.data_ptr(), (int)S,
-                                             (int)(total / S), (int)hq, (int)hkv, (int)d, (int)tpp, num_pages, (int)mp, (float)scale,
-                                             code | (out_f32 ? PAL_OUT_F32 : 0), impl, ws, ws_bytes, stream);
+  const int dt = code | (out_f32 ? PAL_OUT_F32 : 0);
+  int rc;
+  if (ragged)
+    rc = pal_paged_attention_prefill_ragged(q.data_ptr(), k.data_ptr(), v.data_ptr(), k_pool.data_ptr(), v_pool.data_ptr(), page_table.data_ptr(),
+                                            static_cast<const int32_t*>(hist.data_ptr()), static_cast<const int32_t*>(cu_seqlens->data_ptr()),
+                                            out.data_ptr(), (int)S, total, max_new_tokens, (int)hq, (int)hkv, (int)d, (int)tpp, num_pages,
+                                            (int)mp, (float)scale, dt, impl, ws, ws_bytes, stream);
+  else
+    rc = pal_paged_attention_prefill(q.data_ptr(), k.data_ptr(), v.data_ptr(), k_pool.data_ptr(), v_pool.data_ptr(), page_table.data_ptr(),
+                                     static_cast<const int32_t*>(hist.data_ptr()), out.data_ptr(), (int)S, per_seq, (int)hq, (int)hkv, (int)d,
+                                     (int)tpp, num_pages, (int)mp, (float)scale, dt, impl, ws, ws_bytes, stream);
   raise_for(rc);
   return py::cast(out);
 }

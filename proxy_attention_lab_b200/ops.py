@@ -538,7 +538,7 @@ def paged_attention_prefill(q_prompt, k_prompt, v_prompt, k_cache_paged, v_cache
         try:
             out = _fast.prefill(q_prompt, k_prompt, v_prompt, k_cache_paged, v_cache_paged, page_table, context_len_arr,
                                 PREFILL_IMPL[impl] if type(impl) is str else impl, 0.0 if scale is None else float(scale),
-                                out_dtype is torch.float32, _WORKSPACES)
+                                out_dtype is torch.float32, _WORKSPACES, None, 0)
         except TypeError:
             out = None
         if out is not None:
@@ -577,6 +577,16 @@ def paged_attention_prefill_ragged(q_prompt, k_prompt, v_prompt, k_cache_paged, 
     is a decode step, so prefill chunks and decode steps can share one call.  ``max_new_tokens`` (the largest count)
     is read back from ``cu_seqlens`` when not given, which synchronises with the device.  Returns ``[T*Hq, D]``.
     """
+    if (_fast is not None and stream is None and max_new_tokens is not None and (out_dtype is None or out_dtype is torch.float32)
+            and (impl in PREFILL_IMPL or type(impl) is int)):
+        try:
+            out = _fast.prefill(q_prompt, k_prompt, v_prompt, k_cache_paged, v_cache_paged, page_table, context_len_arr,
+                                PREFILL_IMPL[impl] if type(impl) is str else impl, 0.0 if scale is None else float(scale),
+                                out_dtype is torch.float32, _WORKSPACES, cu_seqlens, int(max_new_tokens))
+        except TypeError:
+            out = None
+        if out is not None:
+            return out
     _need_cuda("cu_seqlens", cu_seqlens)
     S, total, hq, hkv, d, tpp, num_pages = _prefill_shapes(q_prompt, k_prompt, v_prompt, k_cache_paged, v_cache_paged,
                                                            page_table, context_len_arr)

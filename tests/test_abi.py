@@ -194,7 +194,7 @@ def test_cpp_front_is_built_and_declines_what_it_does_not_handle():
     assert ops._fast is not None
     x = torch.zeros((2, 4, 64), dtype=torch.float16)
     assert ops._fast.decode(x, x, x, x, x, 0, 0.0, False, {}, None, None) is None
-    assert ops._fast.prefill(x, x, x, x, x, x, x, 0, 0.0, False, {}) is None
+    assert ops._fast.prefill(x, x, x, x, x, x, x, 0, 0.0, False, {}, None, 0) is None
     assert ops._fast.fill(x, x, x, x, x, None, None) is False
     with pytest.raises(RuntimeError):
         ops.paged_attention_decode(x, x, x, x, x)

@@ -149,12 +149,14 @@ def test_cpp_front_and_ctypes_path_agree(pal, cuda, monkeypatch):
     qp, kn, vn = mk(S * 70, hq, d), mk(S * 70, hkv, d), mk(S * 70, hkv, d)
     nk, nv = mk(S, hkv, d), mk(S, hkv, d)
     slots = torch.tensor([5, 77, 300], dtype=torch.int64, device=cuda)
+    cu = torch.tensor([0, 130, 131, 210], dtype=torch.int32, device=cuda)  # ragged view of the same 210 prompt rows
 
     def run_all():
         k2, v2 = kp.clone(), vp.clone()
         outs = [pal.paged_attention_decode(q, kp, vp, table, lens), pal.paged_attention_decode(q, kp, vp, table, lens, partition_pages=2),
                 pal.paged_attention_decode(q, kp, vp, table, lens, out_dtype=torch.float32),
                 pal.paged_attention_prefill(qp, kn, vn, kp, vp, table, lens),
+                pal.paged_attention_prefill_ragged(qp, kn, vn, kp, vp, table, lens, cu, max_new_tokens=130),
                 pal.paged_attention_decode_append(nk, nv, q, k2, v2, table, lens)]
         pal.fill_kv_pages(nk, nv, k2, v2, slots)
         pal.fill_kv_pages(nk, nv, k2, v2, table, lens - 1, torch.arange(S, dtype=torch.int32, device=cuda))
