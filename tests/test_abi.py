@@ -198,3 +198,19 @@ def test_cpp_front_is_built_and_declines_what_it_does_not_handle():
     assert ops._fast.fill(x, x, x, x, x, None, None) is False
     with pytest.raises(RuntimeError):
         ops.paged_attention_decode(x, x, x, x, x)
+
+
+def test_prefill_workspace_plans_the_history_split_from_the_shape():
+    """pal_prefill_workspace_bytes: the header alone for batches that fill the GPU (and for head_dim 256, which runs the
+    two-CTA kernel), header + fp32 partial triples - rows x parts x (D + 2) floats, at most 32 MB - for the few-CTA batches
+    that the tcgen05 kernel cuts along the history."""
+    from proxy_attention_lab_b200 import _lib
+
+    f = _lib.lib.pal_prefill_workspace_bytes
+    assert f(8, 2048, 32, 8, 128) == 256 and f(64, 16, 32, 8, 128) == 256 and f(1, 1, 8, 2, 256) == 256
+    one = f(1, 1, 8, 2, 128)  # 4 CTAs: 16 parts at most
+    assert one == 256 + 1 * 1 * 8 * 16 * 130 * 4
+    big = f(1, 128, 32, 8, 128)  # 16 CTAs -> 9 parts
+    assert big == 256 + 128 * 32 * 9 * 130 * 4
+    assert f(4, 128, 32, 8, 128) - 256 <= 32 << 20
+    assert f(0, 16, 8, 2, 128) == 256
