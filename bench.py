@@ -749,7 +749,14 @@ def measure(w, env, peaks, steps, warmup, blocks, e2e=True):
 
 # DRAM bytes per launch from `ncu --set full` captures of the same workloads, not measured in this run; fill_append is
 # 0.904 x its algorithmic bytes (captured on the reduced case; the traffic grows with the tokens).
-PROFILED_TRAFFIC = {"decode_8b": 1.3866e9, "decode_8b_append": 1.3889e9}
+PROFILED_TRAFFIC = {"decode_8b": 1.3866e9, "decode_8b_append": 1.3889e9, "fill": 2.49e9}
+
+
+def profiled_traffic(name, alg_bytes):
+    """DRAM bytes per launch of workload `name` from the committed ncu summaries (None where there is no capture)."""
+    if name == "fill_append":
+        return 0.904 * alg_bytes
+    return PROFILED_TRAFFIC.get(name)
 
 EXTRA_SINGLE = ["prefill_8b", "prefill_ragged", "prefill_d256", "decode_8b_append", "decode_70b", "decode_70b_auto", "fill", "fill_append"]
 EXTRA_MULTI = ["decode_70b", "decode_70b_auto", "decode_70b_ctx", "decode_70b_ctx_fused", "decode_70b_ctx_fused_auto", "prefill_8b"]
@@ -800,9 +807,7 @@ def main():
     line.update(head.extra_cfg)  # how the workload is spread over the GPUs, beside `config` (which both arms share)
     if "cuda_graph" in rec:
         line["cuda_graph"] = rec["cuda_graph"]
-    traffic = PROFILED_TRAFFIC.get(args.workload) if env.world == 1 else None
-    if args.workload == "fill_append" and env.world == 1:
-        traffic = 0.904 * head.alg_per_step
+    traffic = profiled_traffic(args.workload, head.alg_per_step) if env.world == 1 else None
     line["roofline"]["traffic"] = traffic
     line["roofline"]["traffic_source"] = "ncu capture of this workload (summary committed with the sources), not measured in this run" if traffic else None
     if env.world == 1 and not args.no_cpu_baseline and env.rank == 0:
@@ -837,6 +842,9 @@ def main():
             w = prepare(name, env, pal, peaks, args)
             w.no_sustained = args.no_sustained
             r = measure(w, env, peaks, steps_n, max(3, min(args.warmup, 5)), x_blocks)
+            t = profiled_traffic(name, w.alg_per_step) if env.world == 1 else None
+            r["roofline"]["traffic"] = t
+            r["roofline"]["traffic_source"] = "ncu capture of this workload (summary committed with the sources), not measured in this run" if t else None
             if env.world > 1 and w.scaling == "strong":
                 # the same problem on ONE GPU, run by every rank at the same time: the N = 1 figure of this very run
                 base_name = "decode_70b" if wcfg["kind"] == "decode" else name
