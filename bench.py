@@ -48,6 +48,9 @@ WORKLOADS = {
                                 desc="latency case, newest token appended in the same launch: batch 4, context U[64,512], 8q/2kv heads, D=128, bf16, TPP=16"),
     "decode_small_append_pair": dict(kind="decode", S=4, lo=64, hi=512, hq=8, hkv=2, d=128, tpp=16, partition_pages=0, append="pair",
                                      desc="latency case as two calls, fill_kv_pages then paged_attention_decode: batch 4, context U[64,512], 8q/2kv heads, D=128, bf16, TPP=16"),
+    "decode_70b_small": dict(kind="decode", S=2, lo=131072, hi=131072, hq=64, hkv=8, d=128, tpp=16, partition_pages=256,
+                             desc="reduced long decode for profiler captures: batch 2, context 131072, 64q/8kv heads, D=128, bf16, TPP=16, "
+                                  "two-pass 256-page partitions"),
     "decode_70b": dict(kind="decode", S=8, lo=131072, hi=131072, hq=64, hkv=8, d=128, tpp=16, partition_pages=256,
                        desc="Llama-3-70B long decode: batch 8, context 131072, 64q/8kv heads, D=128, bf16, TPP=16, two-pass 256-page partitions"),
     "decode_70b_auto": dict(kind="decode", S=8, lo=131072, hi=131072, hq=64, hkv=8, d=128, tpp=16, partition_pages=-1,
@@ -756,6 +759,8 @@ def profiled_traffic(name, alg_bytes):
     """DRAM bytes per launch of workload `name` from the committed ncu summaries (None where there is no capture)."""
     if name == "fill_append":
         return 0.904 * alg_bytes
+    if name in ("decode_70b", "decode_70b_auto", "decode_70b_small"):
+        return 1.0065 * alg_bytes  # captured on the batch-2 case; one read of every page plus the partial triples
     return PROFILED_TRAFFIC.get(name)
 
 EXTRA_SINGLE = ["prefill_8b", "prefill_ragged", "prefill_d256", "decode_8b_append", "decode_70b", "decode_70b_auto", "fill", "fill_append"]
@@ -844,7 +849,7 @@ def main():
             r = measure(w, env, peaks, steps_n, max(3, min(args.warmup, 5)), x_blocks)
             t = profiled_traffic(name, w.alg_per_step) if env.world == 1 else None
             r["roofline"]["traffic"] = t
-            r["roofline"]["traffic_source"] = "ncu capture of this workload (summary committed with the sources), not measured in this run" if t else None
+            r["roofline"]["traffic_source"] = "ncu capture of this workload or of its reduced case, scaled (summary committed with the sources), not measured in this run" if t else None
             if env.world > 1 and w.scaling == "strong":
                 # the same problem on ONE GPU, run by every rank at the same time: the N = 1 figure of this very run
                 base_name = "decode_70b" if wcfg["kind"] == "decode" else name
