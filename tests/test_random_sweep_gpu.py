@@ -139,3 +139,36 @@ def test_fill_random(pal, cuda, seed):
     assert torch.equal(gk.cpu().view(torch.int16), ek.view(torch.int16)) and torch.equal(gv.cpu().view(torch.int16), ev.view(torch.int16))
     sk, sv = pal.fill_kv_pages(keys.to(cuda), vals.to(cuda), k.to(cuda), v.to(cuda), slots.to(cuda))
     assert torch.equal(sk.cpu().view(torch.int16), ek.view(torch.int16)) and torch.equal(sv.cpu().view(torch.int16), ev.view(torch.int16))
+
+
+@pytest.mark.parametrize("seed", range(40))
+def test_prefill_kernels_agree_random(pal, cuda, seed):
+    """The prefill kernels against each other on random problems (head_dim 128 / 256, both page sizes, groups of 1-8, 1-5
+    sequences of 1-1024 new tokens over histories around every boundary): the two-CTA kernel equals the one-CTA kernel bit for
+    bit wherever both do the same arithmetic (heads paired or float16, and no history split for that shape), and every
+    tcgen05 form stays within two output roundings of the mma.sync kernel; no bounded wait expires."""
+    from cases import make_prefill_case
+    from proxy_attention_lab_b200._lib import lib
+
+    rng = random.Random(5000 + seed)
+    d = rng.choice([128, 256, 256])
+    tpp = rng.choice([16, 32])
+    hkv = rng.choice([1, 2, 4])
+    group = rng.choice([2, 4, 8] if d == 128 else [1, 2, 3, 4])
+    S = rng.choice([1, 2, 3, 5])
+    n = rng.choice([1, 17, 64, 128, 129, 300, 700, 1024])
+    hist = [rng.choice([0, 1, 15, 63, 64, 65, 127, 128, 500, 1000, 2049, rng.randint(0, 3000)]) for _ in range(S)]
+    dtype = rng.choice([torch.float16, torch.bfloat16])
+    case = make_prefill_case(seed, hist, n, hkv * group, hkv, d, tpp=tpp, dtype=dtype)
+    t = {k: getattr(case, k).to(cuda) for k in ("q", "k_new", "v_new", "k_pool", "v_pool", "page_table", "hist")}
+    run = lambda impl: pal.paged_attention_prefill(t["q"], t["k_new"], t["v_new"], t["k_pool"], t["v_pool"], t["page_table"], t["hist"], impl=impl)
+    pair, single, auto, mma = run("tcgen05_pair"), run("tcgen05_single"), run("tcgen05"), run("mma")
+    torch.cuda.synchronize()
+    pal.check_status()
+    split = lib.pal_prefill_workspace_bytes(S, n, hkv * group, hkv, d) > 256
+    scale = mma.float().abs().max().item()
+    if (group % 2 == 0 or dtype == torch.float16) and not split:
+        assert torch.equal(pair, single)
+    for other in (pair, single, auto):
+        assert torch.isfinite(other.float()).all()
+        assert (other.float() - mma.float()).abs().max().item() <= 2 * TOL + 2.0 ** -7 * scale
